@@ -1,0 +1,65 @@
+"""ctypes binding of ``libdynaflow_b200.so`` (declarations: ``include/dynaflow_b200.h``).
+
+There is no fallback: if the library has not been built, importing this module
+raises, and so does every op of the package.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libdynaflow_b200.so")
+
+
+class NativeLibraryMissing(RuntimeError):
+    pass
+
+
+class df_status_t(ctypes.Structure):
+    _fields_ = [("code", ctypes.c_uint32), ("where", ctypes.c_uint32),
+                ("block", ctypes.c_uint32), ("aux", ctypes.c_uint32)]
+
+
+_vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+
+# name -> (restype, argtypes); must list every symbol the public header declares
+SIGNATURES: dict[str, tuple] = {
+    "df_version": (_i, []),
+    "df_last_error": (ctypes.c_char_p, []),
+    "df_set_timeout_ms": (_i, [_i]),
+    "df_sm_count": (_i, []),
+    "df_status_read": (_i, [_vp, ctypes.POINTER(df_status_t), _vp]),
+    "df_status_clear": (_i, [_vp, _vp]),
+    "df_gemm_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
+    "df_gateup_silu_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
+    "df_mlp_workspace_bytes": (_sz, [_i, _i, _i]),
+    "df_mlp_gated_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+}
+
+_lib = None
+
+
+def lib_path() -> str:
+    return _LIB_PATH
+
+
+def load() -> ctypes.CDLL:
+    """Loads the shared library once and attaches the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(_LIB_PATH):
+        raise NativeLibraryMissing(
+            f"{_LIB_PATH} is missing: build it with `python -m dynaflow_b200.csrc.build` "
+            "(dynaflow_b200 has no CPU or PyTorch fallback)")
+    lib = ctypes.CDLL(_LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    return load().df_last_error().decode("utf-8", "replace")

@@ -1,0 +1,393 @@
+// Gated-MLP kernels for sm_100a: persistent, warp-specialised bf16 GEMM tiles
+// on tcgen05 with accumulators in tensor memory, operands staged by TMA.
+//
+//   mode PLAIN  : C[M,N]  = A[M,K] * B[N,K]^T
+//   mode GATEUP : Hd[M,I] = silu(X * Wg^T) (.) (X * Wu^T)
+//
+// One CTA per SM, 256 threads:
+//   warp 0      TMA producer (one lane): fills a 4-stage ring of
+//               {A 128x64, B 256x64} bf16 tiles, 128-byte swizzled
+//   warp 1      MMA issuer (one lane): 4 x tcgen05.mma 128x256x16 per stage
+//               into one of two 256-column fp32 accumulators
+//   warp 2      allocates / frees the 512 tensor-memory columns
+//   warps 4..7  epilogue: tcgen05.ld of the finished accumulator, SiLU*mul or
+//               plain conversion, 16-byte global stores; runs under the MMAs
+//               of the next tile thanks to the second accumulator
+//
+// In GATEUP mode the B stage is two 128-row boxes, rows [i0,i0+128) of W_gate
+// and of W_up, so the accumulator holds gate in columns [0,128) and up in
+// [128,256) for the same 128 output columns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/dynaflow_b200.h"
+#include "host_util.h"
+#include "ptx.cuh"
+
+namespace df {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int ACC_COLS = 256;  // fp32 accumulator columns per tile (= MMA N)
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_HALF_BYTES = 128 * BK * 2;
+constexpr int B_BYTES = 2 * B_HALF_BYTES;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int GEMM_THREADS = 256;
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+enum : int { MODE_PLAIN = 0, MODE_GATEUP = 1 };
+enum : unsigned { WHERE_PRODUCER = 1, WHERE_MMA_FULL = 2, WHERE_MMA_TMEM = 3, WHERE_EPILOGUE = 4 };
+
+struct GemmParams {
+  int M, N, K;  // N = output columns (I in GATEUP mode)
+  int ldc;
+  int tiles_m, tiles_n, num_tiles, num_kb, group_m;
+  unsigned long long timeout_ns;
+  __nv_bfloat16* C;
+  Status* status;
+};
+
+// Tile order: groups of `group_m` row panels; inside a group the row panel
+// varies fastest, so the CTAs of one wave share few distinct A and B tiles
+// and those stay in L2.
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int t, int& m_blk, int& n_blk) {
+  const int per_group = p.group_m * p.tiles_n;
+  const int group = t / per_group;
+  const int within = t - group * per_group;
+  const int first_m = group * p.group_m;
+  const int gm = min(p.group_m, p.tiles_m - first_m);
+  m_blk = first_m + within % gm;
+  n_blk = within / gm;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+template <int MODE>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
+               const __grid_constant__ CUtensorMap tm_b1, const GemmParams p) {
+  constexpr int BN_OUT = (MODE == MODE_GATEUP) ? 128 : 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 128);
+    }
+    *abort_flag = 0u;
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b0);
+    tma_prefetch_desc(&tm_b1);
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  const uint32_t tmem_base = *tmem_slot;
+  const Deadline dl{globaltimer_ns() + p.timeout_ns, abort_flag, p.status};
+
+  if (warp == 0) {
+    // ------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+        int m_blk, n_blk;
+        tile_coords(p, t, m_blk, n_blk);
+        const int m0 = m_blk * BM;
+        const int n0 = n_blk * BN_OUT;
+        const int y1 = (MODE == MODE_GATEUP) ? n0 : n0 + 128;
+        const CUtensorMap* map1 = (MODE == MODE_GATEUP) ? &tm_b1 : &tm_b0;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, dl, WHERE_PRODUCER, t)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          mbar_expect_tx(&full[stage], STAGE_BYTES);
+          tma_load_2d(sa, &tm_a, &full[stage], kb * BK, m0);
+          tma_load_2d(sb, &tm_b0, &full[stage], kb * BK, n0);
+          tma_load_2d(sb + B_HALF_BYTES, map1, &full[stage], kb * BK, y1);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // -------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, ACC_COLS);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t aphase = (it >> 1) & 1u;
+        if (!mbar_wait(&tempty[acc], aphase ^ 1u, dl, WHERE_MMA_TMEM, t)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * ACC_COLS);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, dl, WHERE_MMA_FULL, t)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
+          const uint64_t da = make_desc_k_sw128(a_addr);
+          const uint64_t db = make_desc_k_sw128(a_addr + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing 16 elements along K = 32 bytes = 2 descriptor units
+            umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(&tfull[acc]);
+      }
+    }
+    __syncwarp();
+  } else if (warp >= 4) {
+    // ---------------------------------------------------------- epilogue
+    const int q = warp - 4;  // == warp % 4: the TMEM lane quarter this warp may read
+    int it = 0;
+    for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++it) {
+      int m_blk, n_blk;
+      tile_coords(p, t, m_blk, n_blk);
+      const int n0 = n_blk * BN_OUT;
+      const int row = m_blk * BM + q * 32 + lane;
+      const int acc = it & 1;
+      const uint32_t aphase = (it >> 1) & 1u;
+      bool ok = mbar_wait(&tfull[acc], aphase, dl, WHERE_EPILOGUE, t);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_acc = tmem_base + static_cast<uint32_t>(acc * ACC_COLS) + (static_cast<uint32_t>(q * 32) << 16);
+      __nv_bfloat16* crow = p.C + static_cast<size_t>(row) * p.ldc;
+      const bool row_ok = row < p.M;
+
+      if (MODE == MODE_GATEUP) {
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(t_acc + c * 32, g);
+          tmem_ld_32x32(t_acc + 128 + c * 32, u);
+          tmem_ld_wait();
+          uint32_t o[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float g0 = round_bf16(__uint_as_float(g[2 * j]));
+            const float g1 = round_bf16(__uint_as_float(g[2 * j + 1]));
+            const float u0 = round_bf16(__uint_as_float(u[2 * j]));
+            const float u1 = round_bf16(__uint_as_float(u[2 * j + 1]));
+            const float h0 = (g0 / (1.0f + expf(-g0))) * u0;
+            const float h1 = (g1 / (1.0f + expf(-g1))) * u1;
+            o[j] = pack_bf16x2(h0, h1);
+          }
+          if (row_ok) {
+            const int col = n0 + c * 32;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (col + v * 8 < p.N) {
+                *reinterpret_cast<uint4*>(crow + col + v * 8) =
+                    make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_acc + c * 32, r);
+          tmem_ld_wait();
+          uint32_t o[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) o[j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+          if (row_ok) {
+            const int col = n0 + c * 32;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (col + v * 8 < p.N) {
+                *reinterpret_cast<uint4*>(crow + col + v * 8) =
+                    make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tempty[acc]);
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    if (*abort_flag) {
+      // error path: give copies and MMAs that are still in flight time to land
+      // before the tensor memory and shared memory are handed back
+      const uint64_t t_stop = globaltimer_ns() + 2000000ull;
+      while (globaltimer_ns() < t_stop) __nanosleep(1000);
+    }
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------- host
+
+static bool make_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                          uint32_t box_rows) {
+  PFN_encodeTiled fn = get_encode_tiled();
+  if (fn == nullptr) return false;
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstride[1] = {ld * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (rows=%llu cols=%llu ld=%llu)", static_cast<int>(r),
+              static_cast<unsigned long long>(rows), static_cast<unsigned long long>(cols),
+              static_cast<unsigned long long>(ld));
+    return false;
+  }
+  return true;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <int MODE>
+static int launch_gemm(const void* a, const void* b0, const void* b1, void* c, int M, int N, int K, int lda, int ldb,
+                       int ldc, int max_ctas, df_status_t* dev_status, void* stream) {
+  if (a == nullptr || b0 == nullptr || b1 == nullptr || c == nullptr || dev_status == nullptr)
+    return fail(DF_EINVAL, "NULL pointer argument");
+  if (M <= 0 || N <= 0 || K <= 0) return fail(DF_EINVAL, "M, N, K must be positive (got %d, %d, %d)", M, N, K);
+  if ((N % 8) != 0 || (K % 8) != 0) return fail(DF_EUNSUPPORTED, "N and K must be multiples of 8 (got %d, %d)", N, K);
+  if (lda < K || ldb < K || ldc < N || (lda % 8) != 0 || (ldb % 8) != 0 || (ldc % 8) != 0)
+    return fail(DF_EINVAL, "leading dimensions must cover the row and be multiples of 8");
+  if (!aligned16(a) || !aligned16(b0) || !aligned16(b1) || !aligned16(c))
+    return fail(DF_EINVAL, "matrix base pointers must be 16-byte aligned");
+
+  int sms = df_sm_count();
+  if (sms <= 0) return fail(DF_ECUDA, "no CUDA device");
+
+  static std::once_flag once[2];
+  static cudaError_t attr_err[2] = {cudaSuccess, cudaSuccess};
+  // the attribute is per device; set it on every call (cheap) so that every device that launches has it
+  attr_err[MODE] = cudaFuncSetAttribute(gemm_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  (void)once;
+  if (attr_err[MODE] != cudaSuccess)
+    return fail(DF_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(attr_err[MODE]));
+
+  CUtensorMap tm_a, tm_b0, tm_b1;
+  if (!make_map_bf16(&tm_a, a, M, K, lda, BM)) return DF_ECUDA;
+  if (!make_map_bf16(&tm_b0, b0, N, K, ldb, 128)) return DF_ECUDA;
+  if (!make_map_bf16(&tm_b1, b1, N, K, ldb, 128)) return DF_ECUDA;
+
+  constexpr int BN_OUT = (MODE == MODE_GATEUP) ? 128 : 256;
+  GemmParams p;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldc = ldc;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (N + BN_OUT - 1) / BN_OUT;
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.num_kb = (K + BK - 1) / BK;
+  p.group_m = 8;
+  p.timeout_ns = timeout_ns();
+  p.C = static_cast<__nv_bfloat16*>(c);
+  p.status = reinterpret_cast<Status*>(dev_status);
+
+  int grid = sms;
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (p.num_tiles < grid) grid = p.num_tiles;
+
+  gemm_tc_kernel<MODE><<<grid, GEMM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tm_a, tm_b0, tm_b1, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(DF_ECUDA, "gemm launch: %s", cudaGetErrorString(e));
+  return DF_OK;
+}
+
+}  // namespace df
+
+extern "C" {
+
+int df_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int lda, int ldb, int ldc, int max_ctas,
+                 df_status_t* dev_status, void* stream) {
+  return df::launch_gemm<df::MODE_PLAIN>(a, b, b, c, M, N, K, lda, ldb, ldc, max_ctas, dev_status, stream);
+}
+
+int df_gateup_silu_bf16(const void* x, const void* w_gate, const void* w_up, void* h, int M, int H, int I, int ldx,
+                        int ldw, int ldh, int max_ctas, df_status_t* dev_status, void* stream) {
+  return df::launch_gemm<df::MODE_GATEUP>(x, w_gate, w_up, h, M, I, H, ldx, ldw, ldh, max_ctas, dev_status, stream);
+}
+
+size_t df_mlp_workspace_bytes(int M, int H, int I) {
+  (void)H;
+  if (M <= 0 || I <= 0) return 0;
+  const size_t h_bytes = static_cast<size_t>(M) * static_cast<size_t>(I) * 2u;
+  return ((h_bytes + 255u) / 256u) * 256u + 256u;
+}
+
+int df_mlp_gated_bf16(const void* x, const void* w_gate, const void* w_up, const void* w_down, void* out,
+                      void* workspace, int M, int H, int I, int max_ctas, df_status_t* dev_status, void* stream) {
+  if (workspace == nullptr) return df::fail(DF_EINVAL, "workspace is NULL");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return df::fail(DF_EINVAL, "workspace must be 256-byte aligned");
+  void* h = workspace;
+  int r = df_gateup_silu_bf16(x, w_gate, w_up, h, M, H, I, H, H, I, max_ctas, dev_status, stream);
+  if (r != DF_OK) return r;
+  return df_gemm_bf16(h, w_down, out, M, H, I, I, I, H, max_ctas, dev_status, stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,170 @@
+"""Tensor-level wrappers over the C ABI (``include/dynaflow_b200.h``).
+
+PyTorch is used for device memory and streams only: every function here hands
+raw device pointers and the current CUDA stream to ``libdynaflow_b200.so``.
+There is no eager/PyTorch fallback; a missing library or a CPU tensor raises.
+
+Weight layout is ``torch.nn.Linear``'s ``[out_features, in_features]``, i.e. the
+layout the subgraphs of a DynaFlow-split model hold their weights in.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _native
+from ._native import df_status_t
+
+DEVICE_ERRORS = {1: "DF_ERR_TIMEOUT", 2: "DF_ERR_PEER"}
+_WHERE = {1: "tma-producer", 2: "mma(full)", 3: "mma(tmem-empty)", 4: "epilogue", 5: "h-ready", 16: "peer-flag"}
+
+
+class DeviceStatusError(RuntimeError):
+    """A kernel reported a bounded wait that ran out (the context stays usable)."""
+
+
+_status: dict[int, torch.Tensor] = {}
+
+
+def _dev_index(t: torch.Tensor) -> int:
+    if not t.is_cuda:
+        raise RuntimeError("dynaflow_b200 ops take CUDA tensors only (there is no CPU path)")
+    return t.device.index if t.device.index is not None else torch.cuda.current_device()
+
+
+def status_block(device: int | torch.device | None = None) -> torch.Tensor:
+    """The per-device 16-byte status block kernels report into."""
+    if device is None:
+        device = torch.cuda.current_device()
+    idx = device.index if isinstance(device, torch.device) else int(device)
+    st = _status.get(idx)
+    if st is None:
+        st = torch.zeros(4, dtype=torch.int32, device=f"cuda:{idx}")
+        _status[idx] = st
+    return st
+
+
+def read_status(device=None) -> df_status_t:
+    """Synchronises the current stream and returns the device status block."""
+    st = status_block(device)
+    host = df_status_t()
+    rc = _native.load().df_status_read(st.data_ptr(), ctypes.byref(host), _stream_ptr(st))
+    if rc != 0:
+        raise RuntimeError(f"df_status_read failed ({rc}): {_native.last_error()}")
+    return host
+
+
+def check_status(device=None) -> None:
+    """Raises ``DeviceStatusError`` if a kernel recorded an error; clears the block."""
+    host = read_status(device)
+    if host.code != 0:
+        st = status_block(device)
+        _native.load().df_status_clear(st.data_ptr(), _stream_ptr(st))
+        raise DeviceStatusError(
+            f"device status {DEVICE_ERRORS.get(host.code, host.code)} at {_WHERE.get(host.where, host.where)} "
+            f"(block {host.block}, aux {host.aux})")
+
+
+def set_timeout_ms(ms: int) -> None:
+    rc = _native.load().df_set_timeout_ms(int(ms))
+    if rc != 0:
+        raise ValueError(_native.last_error())
+
+
+def _stream_ptr(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed ({rc}): {_native.last_error()}")
+
+
+def _require_bf16_2d(name: str, t: torch.Tensor) -> None:
+    if t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{name} must be a 2-D bf16 tensor with unit inner stride, got "
+                         f"{t.dtype} {tuple(t.shape)} strides {t.stride()}")
+
+
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, max_ctas: int = 0) -> torch.Tensor:
+    """``out[M,N] = a[M,K] @ b[N,K].T`` (``b`` in ``nn.Linear`` layout)."""
+    _require_bf16_2d("a", a)
+    _require_bf16_2d("b", b)
+    M, K = a.shape
+    N, Kb = b.shape
+    if K != Kb:
+        raise ValueError(f"inner dimensions differ: a is {tuple(a.shape)}, b is {tuple(b.shape)}")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    _require_bf16_2d("out", out)
+    if tuple(out.shape) != (M, N):
+        raise ValueError(f"out must be {(M, N)}, got {tuple(out.shape)}")
+    if M == 0:
+        return out
+    _dev_index(a)
+    st = status_block(a.device)
+    rc = _native.load().df_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+                                     out.stride(0), max_ctas, st.data_ptr(), _stream_ptr(a))
+    _check(rc, "df_gemm_bf16")
+    return out
+
+
+def gateup_silu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, out: torch.Tensor | None = None,
+                max_ctas: int = 0) -> torch.Tensor:
+    """``silu(x @ w_gate.T) * (x @ w_up.T)`` with the SiLU*mul fused into the GEMM epilogue."""
+    _require_bf16_2d("x", x)
+    _require_bf16_2d("w_gate", w_gate)
+    _require_bf16_2d("w_up", w_up)
+    M, H = x.shape
+    I = w_gate.shape[0]
+    if tuple(w_gate.shape) != (I, H) or tuple(w_up.shape) != (I, H) or w_gate.stride(0) != w_up.stride(0):
+        raise ValueError("w_gate and w_up must both be [I, H] with equal row strides")
+    if out is None:
+        out = torch.empty((M, I), dtype=torch.bfloat16, device=x.device)
+    _require_bf16_2d("out", out)
+    if M == 0:
+        return out
+    _dev_index(x)
+    st = status_block(x.device)
+    rc = _native.load().df_gateup_silu_bf16(x.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), out.data_ptr(), M, H, I,
+                                            x.stride(0), w_gate.stride(0), out.stride(0), max_ctas, st.data_ptr(),
+                                            _stream_ptr(x))
+    _check(rc, "df_gateup_silu_bf16")
+    return out
+
+
+def mlp_workspace_bytes(M: int, H: int, I: int) -> int:
+    return int(_native.load().df_mlp_workspace_bytes(M, H, I))
+
+
+def gated_mlp(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
+              out: torch.Tensor | None = None, workspace: torch.Tensor | None = None,
+              max_ctas: int = 0) -> torch.Tensor:
+    """``(silu(x @ w_gate.T) * (x @ w_up.T)) @ w_down.T`` for one nano-batch of rows."""
+    for name, t in (("x", x), ("w_gate", w_gate), ("w_up", w_up), ("w_down", w_down)):
+        _require_bf16_2d(name, t)
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    M, H = x.shape
+    I = w_gate.shape[0]
+    if tuple(w_gate.shape) != (I, H) or tuple(w_up.shape) != (I, H) or tuple(w_down.shape) != (H, I):
+        raise ValueError("expected w_gate, w_up: [I, H] and w_down: [H, I]")
+    if out is None:
+        out = torch.empty((M, H), dtype=torch.bfloat16, device=x.device)
+    if not out.is_contiguous() or tuple(out.shape) != (M, H) or out.dtype != torch.bfloat16:
+        raise ValueError("out must be a contiguous bf16 [M, H] tensor")
+    if M == 0:
+        return out
+    need = mlp_workspace_bytes(M, H, I)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=x.device)
+    if workspace.numel() * workspace.element_size() < need:
+        raise ValueError(f"workspace too small: need {need} bytes")
+    _dev_index(x)
+    st = status_block(x.device)
+    rc = _native.load().df_mlp_gated_bf16(x.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), w_down.data_ptr(),
+                                          out.data_ptr(), workspace.data_ptr(), M, H, I, max_ctas, st.data_ptr(),
+                                          _stream_ptr(x))
+    _check(rc, "df_mlp_gated_bf16")
+    return out

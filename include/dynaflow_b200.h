@@ -1,0 +1,118 @@
+/*
+ * dynaflow_b200 -- C ABI of the B200 (sm_100a) execution backend for DynaFlow's
+ * batch-split, overlapped transformer-layer schedule.
+ *
+ * Conventions
+ *   - plain C types only; every pointer named "dev" or documented as device
+ *     memory is a CUDA device pointer owned by the caller;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *   - return value: 0 = launched / done; < 0 = argument or CUDA API error
+ *     (df_last_error() has the text); device-side failures (a bounded wait
+ *     that ran out) are reported asynchronously in the df_status_t block the
+ *     caller passed, never by trapping or spinning forever;
+ *   - no entry point allocates or frees device memory, none synchronises the
+ *     host with the device unless its comment says so;
+ *   - bf16 matrices are row-major with an explicit leading dimension counted
+ *     in elements; all base pointers 16-byte aligned, leading dimensions a
+ *     multiple of 8 elements.
+ *
+ * The library has no CPU fallback: on a machine without an sm_100 GPU the
+ * compute entry points return DF_ECUDA.
+ */
+#ifndef DYNAFLOW_B200_H_
+#define DYNAFLOW_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DF_ABI_VERSION 1
+
+/* host-side return codes */
+#define DF_OK 0
+#define DF_EINVAL (-1)       /* bad shape, alignment or NULL pointer */
+#define DF_ECUDA (-2)        /* a CUDA runtime / driver call failed   */
+#define DF_EUNSUPPORTED (-3) /* shape outside what the kernels cover  */
+
+/* device-side codes, written to df_status_t.code */
+#define DF_ERR_NONE 0u
+#define DF_ERR_TIMEOUT 1u /* a bounded wait ran past the deadline */
+#define DF_ERR_PEER 2u    /* a peer rank never raised its flag     */
+
+/* Asynchronous device status block (16 bytes of device memory, zero = ok). */
+typedef struct df_status {
+  uint32_t code;  /* first DF_ERR_* recorded since the last clear          */
+  uint32_t where; /* which wait gave up (producer / mma / epilogue / flag) */
+  uint32_t block; /* blockIdx.x of the reporting CTA                       */
+  uint32_t aux;   /* tile index or peer rank                               */
+} df_status_t;
+
+/* ------------------------------------------------------------------ basics */
+
+/* ABI version of the loaded library (DF_ABI_VERSION). */
+int df_version(void);
+
+/* Text of the last host-side error on the calling thread ("" if none). */
+const char* df_last_error(void);
+
+/* Deadline, in milliseconds from kernel start, that bounds every device-side
+ * wait of kernels launched afterwards (default 2000). The reference has no
+ * counterpart: its device waits are unbounded
+ * (examples/ae/scheduler/vllm/tokenweave-kernels/include/tokenweave_multimem_utils.cuh:157-169). */
+int df_set_timeout_ms(int ms);
+
+/* Number of SMs of the current device (grid sizing of the persistent kernels). */
+int df_sm_count(void);
+
+/* Copies the status block to the host; synchronises `stream`. */
+int df_status_read(const df_status_t* dev_status, df_status_t* host_out, void* stream);
+
+/* Zeroes the status block on `stream` (asynchronous). */
+int df_status_clear(df_status_t* dev_status, void* stream);
+
+/* --------------------------------------------------------------- gated MLP
+ *
+ * Replaces, for one nano-batch, the three operators a host model runs inside a
+ * DynaFlow compute subgraph: gate_up linear -> SiLU*mul -> down linear
+ * (operator statement: examples/ae/up-silu-overlap.cu:75-82; subgraph
+ * execution: dynaflow/runtime/engine.py:320-381).
+ *
+ * Weights use the torch.nn.Linear layout [out_features, in_features]:
+ *   w_gate, w_up : [I, H]      w_down : [H, I]
+ *   x : [M, H]   out : [M, H]  h (intermediate) : [M, I]
+ */
+
+/* C[M,N] = A[M,K] * B[N,K]^T, bf16 in, fp32 accumulate, bf16 out.
+ * The plain linear layer of a subgraph (down / o / qkv projections).
+ * max_ctas <= 0 means "one CTA per SM". */
+int df_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int lda, int ldb, int ldc,
+                 int max_ctas, df_status_t* dev_status, void* stream);
+
+/* h[M,I] = silu(x * w_gate^T) (.) (x * w_up^T): gate and up accumulators of the
+ * same output columns live side by side in tensor memory and the SiLU*mul runs
+ * in the epilogue, so the [M,2I] gate_up activation never exists in HBM.
+ * Rounding points follow the reference operator chain: the two GEMM results
+ * are rounded to bf16, the product silu(g)*u is computed in fp32 with expf and
+ * rounded once to bf16. */
+int df_gateup_silu_bf16(const void* x, const void* w_gate, const void* w_up, void* h, int M, int H, int I,
+                        int ldx, int ldw, int ldh, int max_ctas, df_status_t* dev_status, void* stream);
+
+/* Bytes of scratch df_mlp_gated_bf16 needs for the bf16 intermediate h[M,I]
+ * plus its tile-ready counters. */
+size_t df_mlp_workspace_bytes(int M, int H, int I);
+
+/* out = (silu(x * w_gate^T) (.) (x * w_up^T)) * w_down^T  for one nano-batch.
+ * `workspace` is caller-owned device memory of df_mlp_workspace_bytes(M,H,I)
+ * bytes, 256-byte aligned; its contents are scratch. */
+int df_mlp_gated_bf16(const void* x, const void* w_gate, const void* w_up, const void* w_down, void* out,
+                      void* workspace, int M, int H, int I, int max_ctas, df_status_t* dev_status,
+                      void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* DYNAFLOW_B200_H_ */
