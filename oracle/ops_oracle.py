@@ -1,0 +1,89 @@
+"""Floating-point side of the hot path, restated with plain PyTorch CPU ops.
+
+Rounding points are those of the operator chain a host model runs inside the
+reference's subgraphs: every operator takes and returns bf16 (or fp32) tensors,
+accumulating in fp32 inside.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+
+def gated_mlp(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+    """``down(silu(gate(x)) * up(x))`` as the chain linear -> silu_and_mul -> linear.
+
+    The SiLU*mul stage reads the (dtype-rounded) GEMM results, computes
+    ``g / (1 + exp(-g)) * u`` in fp32 and rounds once
+    (``examples/ae/up-silu-overlap.cu:75-90``). Weights are ``[out, in]``."""
+    g = F.linear(x, w_gate)
+    u = F.linear(x, w_up)
+    h = silu_mul(g, u)
+    return F.linear(h, w_down)
+
+
+def silu_mul(g: torch.Tensor, u: torch.Tensor) -> torch.Tensor:
+    gf, uf = g.float(), u.float()
+    return ((gf / (1.0 + torch.exp(-gf))) * uf).to(g.dtype)
+
+
+def gated_mlp_hf(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+    """The same MLP written the way a Hugging Face decoder block does it
+    (``act_fn(gate_proj(x)) * up_proj(x)``: SiLU and the product each round to the
+    tensor dtype). This is the form the reference package executes on CPU for the
+    golden vectors; in fp32 it equals ``gated_mlp`` up to rounding of the division."""
+    return F.linear(F.silu(F.linear(x, w_gate)) * F.linear(x, w_up), w_down)
+
+
+def allreduce_add_rmsnorm(partials: list[torch.Tensor], residual: torch.Tensor | None, weight: torch.Tensor,
+                          eps: float = 1e-5) -> tuple[torch.Tensor, torch.Tensor]:
+    """``y = sum_r partials[r]; r' = y + residual; out = rmsnorm(r') * weight``.
+
+    Call-site semantics: ``examples/ae/scheduler/vllm/nanoflow.py:171-211`` (residual
+    is zeros when absent; eps 1e-5) and the in-tree kernel
+    ``tokenweave-kernels/csrc/tokenweave.cu:38-113``: the cross-rank sum accumulates
+    in fp32 and is rounded to bf16, the residual add is a bf16 add, the new residual
+    is stored in bf16, the sum of squares is fp32 over the bf16 residual, and the
+    normalised value is rounded to bf16 before the multiplication by the weight
+    (``temp *= s_variance; temp *= weight`` on bf16 vectors).
+    Returns ``(out, new_residual)``."""
+    dtype = partials[0].dtype
+    acc = torch.zeros_like(partials[0], dtype=torch.float32)
+    for p in partials:
+        acc += p.float()
+    y = acc.to(dtype)
+    if residual is None:
+        residual = torch.zeros_like(y)
+    new_res = (y.float() + residual.float()).to(dtype)
+    var = new_res.float().pow(2).sum(dim=-1, keepdim=True) / new_res.shape[-1]
+    inv = torch.rsqrt(var + eps)
+    normed = (new_res.float() * inv).to(dtype)
+    out = (normed.float() * weight.float()).to(dtype)
+    return out, new_res
+
+
+def top2_route(router_logits: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """Mixtral-style routing: softmax over experts in fp32, top-2, renormalise.
+    Returns ``(weights [T,2] fp32, expert ids [T,2] int64)``; ties resolve to the
+    lower expert index (``torch.topk`` on CPU)."""
+    probs = torch.softmax(router_logits.float(), dim=-1)
+    w, ids = torch.topk(probs, 2, dim=-1)
+    w = w / w.sum(dim=-1, keepdim=True)
+    return w, ids
+
+
+def moe_layer(x: torch.Tensor, router_logits: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
+              w_down: torch.Tensor) -> torch.Tensor:
+    """Top-2 mixture of gated-MLP experts: dispatch = index gather of the rows routed
+    to an expert, combine = weighted scatter-add in fp32, rounded once at the end.
+    ``w_gate, w_up: [E, I, H]``, ``w_down: [E, H, I]``. The three-way operator split
+    dispatch / expert / combine is ``examples/ae/patch/vllm.patch:308-379, 423-527``."""
+    weights, ids = top2_route(router_logits)
+    out = torch.zeros(x.shape, dtype=torch.float32)
+    for e in range(w_gate.shape[0]):
+        rows, slot = torch.nonzero(ids == e, as_tuple=True)
+        if rows.numel() == 0:
+            continue
+        y = gated_mlp(x[rows], w_gate[e], w_up[e], w_down[e])
+        out.index_add_(0, rows, y.float() * weights[rows, slot].unsqueeze(-1))
+    return out.to(x.dtype)

@@ -1,0 +1,33 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+REFERENCE = "/root/reference"
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
+    config.addinivalue_line("markers", "reference: needs the reference tree (build container only)")
+
+
+def pytest_collection_modifyitems(config, items):
+    have_ref = os.path.isdir(os.path.join(REFERENCE, "dynaflow"))
+    for item in items:
+        if "reference" in item.keywords and not have_ref:
+            item.add_marker(pytest.mark.skip(reason="reference tree not present"))
+
+
+@pytest.fixture(scope="session")
+def native_lib():
+    """Builds (if stale) and loads the C-ABI library."""
+    from dynaflow_b200 import _native
+    from dynaflow_b200.csrc import build as build_mod
+
+    build_mod.build()
+    return _native.load()
