@@ -1,0 +1,324 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: the batch-split gated-MLP layer step on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the single-GPU configuration of the fused-MLP metric): X [16384, 4096]
+bf16 N(0,1), W_gate / W_up [14336, 4096], W_down [4096, 14336] bf16 N(0, 0.02),
+out = (silu(X W_gate^T) * (X W_up^T)) W_down^T, executed as two micro-batches of
+8192 rows. One "step" is one pass over the 16384 rows. With N > 1 the layer is
+tensor-parallel (intermediate dimension sharded N ways, partial outputs reduced
+across ranks, the reduction of micro-batch i overlapped with the GEMMs of i+1).
+
+Prints ONE JSON line on rank 0. ``value`` is tokens/s with inputs resident in HBM,
+``e2e`` the same metric with host buffers and the copies inside the timed region.
+``--impl reference`` times the CPU restatement of the reference's operator chain
+on the host cores instead (a bounded sample per step).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+H, I = 4096, 14336
+ROWS = 16384
+MICRO_BATCHES = 2
+METRIC = "prefill tokens/sec through the fused gated-MLP layer (2 micro-batches)"
+
+
+def measured_peaks() -> tuple[dict, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int, period_ms: int = 50) -> None:
+        self.samples: list[tuple[float, list[str]]] = []
+        self._proc = None
+        self._thread = None
+        try:
+            self._proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", str(period_ms),
+                 "-i", str(gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self._thread = threading.Thread(target=self._pump, daemon=True)
+            self._thread.start()
+        except OSError:
+            self._proc = None
+
+    def _pump(self) -> None:
+        assert self._proc is not None and self._proc.stdout is not None
+        for line in self._proc.stdout:
+            self.samples.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self) -> None:
+        if self._proc is not None:
+            self._proc.terminate()
+            try:
+                self._proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self._proc.kill()
+
+    def summary(self, t0: float, t1: float) -> dict:
+        rows = [c for t, c in self.samples if t0 <= t <= t1 and len(c) >= 7]
+        window = "timed region"
+        if not rows:
+            rows = [c for _, c in self.samples if len(c) >= 7]
+            window = "whole run (timed region shorter than the sampling period)"
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "window": "nvidia-smi unavailable"}
+        mhz = [float(c[0]) for c in rows if c[0].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(c[3 + i].lower().startswith("active") for c in rows)]
+        power = [float(c[2]) for c in rows if c[2].replace(".", "").isdigit()]
+        return {"sm_mhz": statistics.median(mhz) if mhz else None, "sm_max_mhz": float(rows[0][1]),
+                "power_w_max": max(power) if power else None, "reasons": reasons, "samples": len(rows),
+                "window": window}
+
+
+# ------------------------------------------------------------------ CPU arm
+def cpu_port_rate(rows: int, repeats: int = 1) -> tuple[float, float]:
+    """Times the oracle's gated MLP (the reference's operator chain restated on
+    PyTorch CPU ops, bf16, all host threads) on ``rows`` rows. Returns (tokens/s, seconds)."""
+    import torch
+
+    from oracle import ops_oracle
+
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(rows, H, generator=g).bfloat16()
+    wg = (torch.randn(I, H, generator=g) * 0.02).bfloat16()
+    wu = (torch.randn(I, H, generator=g) * 0.02).bfloat16()
+    wd = (torch.randn(H, I, generator=g) * 0.02).bfloat16()
+    best = float("inf")
+    with torch.inference_mode():
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            ops_oracle.gated_mlp(x, wg, wu, wd)
+            best = min(best, time.perf_counter() - t0)
+    return rows / best, best
+
+
+def cpu_weights():
+    import torch
+
+    g = torch.Generator().manual_seed(0)
+    wg = (torch.randn(I, H, generator=g) * 0.02).bfloat16()
+    wu = (torch.randn(I, H, generator=g) * 0.02).bfloat16()
+    wd = (torch.randn(H, I, generator=g) * 0.02).bfloat16()
+    return wg, wu, wd
+
+
+def run_reference_arm(args) -> None:
+    """CPU implementation of the path on the host cores, all threads, bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+
+    from oracle import ops_oracle
+
+    cores = torch.get_num_threads()
+    wg, wu, wd = cpu_weights()
+    g = torch.Generator().manual_seed(1)
+    probe = torch.randn(16, H, generator=g).bfloat16()
+    with torch.inference_mode():
+        ops_oracle.gated_mlp(probe, wg, wu, wd)
+        t0 = time.perf_counter()
+        ops_oracle.gated_mlp(probe, wg, wu, wd)
+        per_row = (time.perf_counter() - t0) / 16
+    budget = min(2.0, 150.0 / max(1, args.steps + args.warmup))
+    rows = int(max(16, min(ROWS, budget / per_row)) // 16 * 16)
+    x = torch.randn(rows, H, generator=g).bfloat16()
+    with torch.inference_mode():
+        for _ in range(args.warmup):
+            ops_oracle.gated_mlp(x, wg, wu, wd)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            ops_oracle.gated_mlp(x, wg, wu, wd)
+        dt = time.perf_counter() - t0
+    value = rows * args.steps / dt
+    sample = f"{rows} of {ROWS} rows per step, {args.steps} steps, bf16, torch CPU"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_config(n_gpus: int) -> dict:
+    return {"workload": f"fused gated MLP, X[{ROWS},{H}] bf16, W_gate/W_up[{I},{H}], W_down[{H},{I}], "
+                        f"{MICRO_BATCHES} micro-batches of {ROWS // MICRO_BATCHES} rows",
+            "rows": ROWS, "hidden": H, "intermediate": I, "micro_batches": MICRO_BATCHES,
+            "parallelism": f"tp{n_gpus}", "l2": "inputs larger than L2 (weights 352 MB + activations 604 MB per step)"}
+
+
+# ------------------------------------------------------------------ GPU arm
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from dynaflow_b200 import ops
+    from dynaflow_b200.layer import TensorParallelGatedMLP
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    layer = TensorParallelGatedMLP(H, I, rank=rank, world=world, max_rows=ROWS // MICRO_BATCHES,
+                                   micro_batches=MICRO_BATCHES, seed=0, device=dev)
+    gen = torch.Generator().manual_seed(1)
+    x_host = torch.randn(ROWS, H, generator=gen).bfloat16().pin_memory()
+    out_host = torch.empty(ROWS, H, dtype=torch.bfloat16).pin_memory()
+    x_dev = x_host.to(dev)
+    out_dev = torch.empty(ROWS, H, dtype=torch.bfloat16, device=dev)
+    cuts = [ROWS * i // MICRO_BATCHES for i in range(MICRO_BATCHES + 1)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+
+    # ---- device-resident: value, and per-kernel times for the roofline
+    for _ in range(args.warmup):
+        layer.forward_device(x_dev, out_dev, cuts)
+    barrier()
+    marks = []
+    t_wall0 = time.time()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        marks.append(layer.forward_device(x_dev, out_dev, cuts, record_kernel_events=True))
+    end.record()
+    barrier()
+    t_wall1 = time.time()
+    ms_step = max_over_ranks(start.elapsed_time(end) / args.steps)
+    gateup_ms = statistics.mean(m0.elapsed_time(m1) for step in marks for (m0, m1, _m2) in step)
+    down_ms = statistics.mean(m1.elapsed_time(m2) for step in marks for (_m0, m1, m2) in step)
+    ops.check_status()
+
+    # ---- end to end: pinned host buffers, copies inside the timed region
+    for _ in range(args.warmup):
+        layer.forward_host(x_host, out_host, cuts)
+    barrier()
+    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s2.record()
+    for _ in range(args.steps):
+        layer.forward_host(x_host, out_host, cuts)
+    e2.record()
+    barrier()
+    e2e_ms = max_over_ranks(s2.elapsed_time(e2) / args.steps)
+    ops.check_status()
+    if sampler is not None:
+        sampler.stop()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_kind = measured_peaks()
+    rows_mb = ROWS // MICRO_BATCHES
+    gateup_flops = 4.0 * rows_mb * H * (I // world)
+    achieved = gateup_flops / (gateup_ms * 1e-3) / 1e12
+    peak = float(peaks["bf16_tflops"])
+    step_flops = 6.0 * ROWS * H * (I // world)
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "gateup_traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as f:
+            traffic = json.load(f).get("dram_bytes_per_launch")
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        _, probe_s = cpu_port_rate(32)
+        rows = int(max(32, min(2048, 12.0 / (probe_s / 32))) // 32 * 32)
+        rate, secs = cpu_port_rate(rows)
+        import torch as _t
+
+        cpu = {"value": rate, "unit": "tokens/s", "cores": _t.get_num_threads(), "kind": "port",
+               "sample": f"{rows} of {ROWS} rows, one pass of the oracle's gated MLP in {secs:.1f} s (bf16, torch CPU)"}
+
+    line = {
+        "metric": METRIC, "value": ROWS / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+        "e2e": {"value": ROWS / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": ROWS * H * 2, "d2h_bytes_per_step": ROWS * H * 2},
+        "gpu_launches": layer.launches_per_step * args.steps,
+        "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel<GATEUP> (gate/up GEMM + SiLU*mul epilogue)",
+                     "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                     "peak_source": f"{peak_kind} cuBLAS bf16 burst", "frac_of_sustained":
+                         achieved / float(peaks.get("bf16_tflops_sustained", peak)),
+                     "frac_of_nominal_2250": achieved / 2250.0, "traffic": traffic,
+                     "flops_per_launch": gateup_flops, "ms_per_launch": gateup_ms,
+                     "down_gemm_tflops": 2.0 * rows_mb * H * (I // world) / (down_ms * 1e-3) / 1e12},
+        "mlp_pct_tensor_peak": 100.0 * step_flops / (ms_step * 1e-3) / 1e12 / peak,
+        "clocks": sampler.summary(t_wall0, t_wall1) if sampler is not None else None,
+        "cpu_baseline": cpu,
+    }
+    if world > 1:
+        line["comm"] = layer.comm_summary()
+        dist.destroy_process_group()
+    print(json.dumps(line))
+
+
+def main() -> None:
+    global ROWS
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--rows", type=int, default=ROWS, help="rows per step (default: the benchmark's 16384; "
+                    "smaller values are for profiler captures only)")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    args = ap.parse_args()
+    if args.rows != ROWS:
+        if args.rows <= 0 or args.rows % (MICRO_BATCHES * 8) != 0:
+            raise SystemExit("--rows must be a positive multiple of 16")
+        ROWS = args.rows
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

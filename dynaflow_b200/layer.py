@@ -1,0 +1,127 @@
+"""The batch-split gated-MLP layer step as a user-facing object.
+
+``TensorParallelGatedMLP`` owns one rank's weight shards, the per-micro-batch
+scratch for the bf16 intermediate, and the streams of the overlapped schedule:
+
+* ``forward_device`` runs the micro-batches back to back on the caller's stream
+  (inputs and outputs resident in HBM);
+* ``forward_host`` takes pinned host buffers: micro-batch ``i`` is copied in, run
+  and copied out on its own stream, so the copies of one micro-batch hide under
+  the GEMMs of the other -- the same interleaving the NanoFlow policy produces
+  for ``network``-tagged subgraphs (``examples/ae/scheduler/hf/nanoflow.py:123-146``).
+
+With ``world > 1`` the intermediate dimension is sharded (gate/up by output rows,
+down by input columns, i.e. Megatron column/row parallel) and the partial outputs
+of a micro-batch are summed across ranks by the peer-memory all-reduce on the
+communication stream while the next micro-batch's GEMMs run.
+"""
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+
+from . import ops
+
+
+class TensorParallelGatedMLP:
+    def __init__(self, hidden: int, intermediate: int, *, rank: int = 0, world: int = 1, max_rows: int,
+                 micro_batches: int = 2, seed: int = 0, device: torch.device | None = None,
+                 weights: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None,
+                 comm: Any | None = None) -> None:
+        if intermediate % world != 0:
+            raise ValueError("the intermediate size must divide evenly across ranks")
+        self.hidden, self.intermediate = hidden, intermediate
+        self.rank, self.world = rank, world
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.micro_batches = micro_batches
+        self.max_rows = max_rows
+        shard = intermediate // world
+        lo, hi = rank * shard, (rank + 1) * shard
+        if weights is None:
+            # full weights N(0, 0.02) from the seed (identical on every rank), then this rank's shard
+            g = torch.Generator().manual_seed(seed)
+            w_gate = (torch.randn(intermediate, hidden, generator=g) * 0.02).bfloat16()
+            w_up = (torch.randn(intermediate, hidden, generator=g) * 0.02).bfloat16()
+            w_down = (torch.randn(hidden, intermediate, generator=g) * 0.02).bfloat16()
+        else:
+            w_gate, w_up, w_down = weights
+        self.w_gate = w_gate[lo:hi].contiguous().to(self.device)
+        self.w_up = w_up[lo:hi].contiguous().to(self.device)
+        self.w_down = w_down[:, lo:hi].contiguous().to(self.device)
+        self.shard = shard
+        ws_bytes = ops.mlp_workspace_bytes(max_rows, hidden, shard)
+        self.workspaces = [torch.empty(ws_bytes, dtype=torch.uint8, device=self.device) for _ in range(micro_batches)]
+        self.h_views = [ws[: max_rows * shard * 2].view(torch.bfloat16).view(max_rows, shard) for ws in self.workspaces]
+        self.streams = [torch.cuda.Stream(device=self.device) for _ in range(micro_batches)]
+        self.staging_in = [torch.empty(max_rows, hidden, dtype=torch.bfloat16, device=self.device)
+                           for _ in range(micro_batches)]
+        self.staging_out = [torch.empty(max_rows, hidden, dtype=torch.bfloat16, device=self.device)
+                            for _ in range(micro_batches)]
+        self.comm = comm
+        if world > 1 and comm is None:
+            raise ValueError("world > 1 needs a communicator (dynaflow_b200.comm.PeerComm)")
+        self.launches_per_step = 2 * micro_batches + (micro_batches if world > 1 else 0)
+
+    # ------------------------------------------------------------------
+    def _mlp(self, x: torch.Tensor, out: torch.Tensor, mb: int, record: bool):
+        rows = x.shape[0]
+        h = self.h_views[mb][:rows]
+        marks = None
+        if record:
+            m0, m1, m2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            m0.record()
+            ops.gateup_silu(x, self.w_gate, self.w_up, out=h)
+            m1.record()
+            ops.gemm_bf16(h, self.w_down, out=out)
+            m2.record()
+            marks = (m0, m1, m2)
+        else:
+            ops.gated_mlp(x, self.w_gate, self.w_up, self.w_down, out=out, workspace=self.workspaces[mb])
+        return marks
+
+    def forward_device(self, x: torch.Tensor, out: torch.Tensor, cuts: list[int], record_kernel_events: bool = False):
+        """``out[cuts[i]:cuts[i+1]] = mlp(x[cuts[i]:cuts[i+1]])`` for every micro-batch ``i``."""
+        marks = []
+        for mb in range(len(cuts) - 1):
+            lo, hi = cuts[mb], cuts[mb + 1]
+            if hi == lo:
+                continue
+            m = self._mlp(x[lo:hi], out[lo:hi], mb % self.micro_batches, record_kernel_events)
+            if self.world > 1:
+                self.comm.all_reduce_async(out[lo:hi], mb)
+            if m is not None:
+                marks.append(m)
+        if self.world > 1:
+            self.comm.join()
+        return marks
+
+    def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, cuts: list[int]) -> None:
+        """Same step from pinned host memory; copies ride on the micro-batch's own stream."""
+        main = torch.cuda.current_stream(self.device)
+        fork = torch.cuda.Event()
+        fork.record(main)
+        joins = []
+        for mb in range(len(cuts) - 1):
+            lo, hi = cuts[mb], cuts[mb + 1]
+            if hi == lo:
+                continue
+            slot = mb % self.micro_batches
+            stream = self.streams[slot]
+            stream.wait_event(fork)
+            with torch.cuda.stream(stream):
+                xin = self.staging_in[slot][: hi - lo]
+                yout = self.staging_out[slot][: hi - lo]
+                xin.copy_(x_host[lo:hi], non_blocking=True)
+                self._mlp(xin, yout, slot, False)
+                if self.world > 1:
+                    self.comm.all_reduce_on_current_stream(yout, slot)
+                out_host[lo:hi].copy_(yout, non_blocking=True)
+                done = torch.cuda.Event()
+                done.record(stream)
+                joins.append(done)
+        for done in joins:
+            main.wait_event(done)
+
+    def comm_summary(self) -> dict:
+        return self.comm.summary() if self.comm is not None else {}

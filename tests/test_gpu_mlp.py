@@ -1,0 +1,135 @@
+"""Parity of the sm_100a gated-MLP kernels (through the C ABI) against the CPU oracle.
+
+Tolerance (bf16, as the task states it): max|a-b| / max|b| <= 2e-2.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-2
+
+
+def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
+    return ((got.float().cpu() - want.float().cpu()).abs().max() / want.float().abs().max()).item()
+
+
+@pytest.fixture(scope="module")
+def ops(native_lib):
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    from dynaflow_b200 import ops as _ops
+
+    return _ops
+
+
+def _rand(shape, scale, seed):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).bfloat16()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (1, 8, 8), (16, 256, 4096), (257, 520, 200), (100, 4096, 1024),
+                                    (384, 264, 14336 // 8)])
+def test_gemm_matches_oracle(ops, M, N, K):
+    a, b = _rand((M, K), 1.0, 1), _rand((N, K), 0.05, 2)
+    got = ops.gemm_bf16(a.cuda(), b.cuda())
+    ops.check_status()
+    want = torch.nn.functional.linear(a.float(), b.float())
+    assert rel_err(got, want) <= TOL
+
+
+def test_gemm_strided_operands_and_output(ops):
+    a_full, b_full = _rand((96, 512), 1.0, 3).cuda(), _rand((264, 512), 0.05, 4).cuda()
+    out_full = torch.zeros(96, 512, dtype=torch.bfloat16, device="cuda")
+    a, b, out = a_full[:, 128:384], b_full[:, 64:320], out_full[:, 8:272]
+    ops.gemm_bf16(a, b, out=out)
+    ops.check_status()
+    want = a.float() @ b.float().T
+    assert rel_err(out, want) <= TOL
+    assert out_full[:, :8].abs().sum() == 0 and out_full[:, 272:].abs().sum() == 0  # nothing outside the view
+
+
+@pytest.mark.parametrize("M,H,I", [(128, 64, 128), (1, 64, 128), (16, 256, 256), (300, 512, 1032), (1000, 1024, 2816)])
+def test_gated_mlp_matches_oracle(ops, M, H, I):
+    from oracle import ops_oracle
+
+    x = _rand((M, H), 1.0, 5)
+    wg, wu, wd = _rand((I, H), 0.05, 6), _rand((I, H), 0.05, 7), _rand((H, I), 0.05, 8)
+    h = ops.gateup_silu(x.cuda(), wg.cuda(), wu.cuda())
+    out = ops.gated_mlp(x.cuda(), wg.cuda(), wu.cuda(), wd.cuda())
+    ops.check_status()
+    g = torch.nn.functional.linear(x, wg)
+    u = torch.nn.functional.linear(x, wu)
+    assert rel_err(h, ops_oracle.silu_mul(g, u)) <= TOL
+    assert rel_err(out, ops_oracle.gated_mlp(x, wg, wu, wd)) <= TOL
+    assert rel_err(out, ops_oracle.gated_mlp_hf(x, wg, wu, wd)) <= TOL
+
+
+def test_gated_mlp_against_reference_golden(ops):
+    z = np.load(os.path.join(GOLDEN, "mlp_split.npz"))
+    t = {k: torch.from_numpy(z[k]).view(torch.bfloat16) for k in z.files}
+    cuts = json.load(open(os.path.join(GOLDEN, "mlp_split.json")))["split"]["split_indices"]
+    dev = {k: v.cuda() for k, v in t.items()}
+    # the reference executed this MLP as two nano-batches cut at `cuts` and concatenated the results
+    parts = [ops.gated_mlp(dev["x"][cuts[i]:cuts[i + 1]], dev["w_gate"], dev["w_up"], dev["w_down"]) for i in range(2)]
+    ops.check_status()
+    assert rel_err(torch.cat(parts), t["out"]) <= TOL
+
+
+def test_empty_nano_batch(ops):
+    x = torch.empty(0, 64, dtype=torch.bfloat16, device="cuda")
+    w = _rand((128, 64), 0.05, 1).cuda()
+    wd = _rand((64, 128), 0.05, 2).cuda()
+    assert ops.gated_mlp(x, w, w, wd).shape == (0, 64)
+    assert ops.gemm_bf16(x, w).shape == (0, 128)
+
+
+def test_micro_batch_split_is_bit_exact_at_full_size(ops):
+    """Size-independent property at the benchmark shape: every output row depends on
+    its own input row only and tiles accumulate in a fixed order, so running the two
+    micro-batches separately gives bit-identical rows to one full-batch run."""
+    M, H, I = 4096, 4096, 14336
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(M, H, device="cuda", generator=g).bfloat16()
+    wg = (torch.randn(I, H, device="cuda", generator=g) * 0.02).bfloat16()
+    wu = (torch.randn(I, H, device="cuda", generator=g) * 0.02).bfloat16()
+    wd = (torch.randn(H, I, device="cuda", generator=g) * 0.02).bfloat16()
+    full = ops.gated_mlp(x, wg, wu, wd)
+    for cut in (M // 2, 1000):
+        parts = torch.cat([ops.gated_mlp(x[:cut].contiguous(), wg, wu, wd), ops.gated_mlp(x[cut:].contiguous(), wg, wu, wd)])
+        assert torch.equal(parts, full)
+    ops.check_status()
+    # scaling the input by 2 scales the gate pre-activation: check linearity of the down projection instead
+    h = ops.gateup_silu(x[:256].contiguous(), wg, wu)
+    y1 = ops.gemm_bf16(h, wd)
+    y2 = ops.gemm_bf16((h.float() * 2).bfloat16(), wd)
+    assert torch.equal((y1.float() * 2).bfloat16(), y2)  # power-of-two scaling is exact in bf16/fp32
+    # sampled rows against the CPU oracle at this size
+    from oracle import ops_oracle
+
+    rows = torch.tensor([0, 1, 127, 128, 2047, 2048, 4095])
+    want = ops_oracle.gated_mlp(x[rows].cpu(), wg.cpu(), wu.cpu(), wd.cpu())
+    assert rel_err(full[rows], want) <= TOL
+
+
+def test_limited_grid_gives_identical_results(ops):
+    x, w, wd = _rand((512, 256), 1.0, 1).cuda(), _rand((1024, 256), 0.05, 2).cuda(), _rand((256, 1024), 0.05, 3).cuda()
+    a = ops.gated_mlp(x, w, w, wd)
+    b = ops.gated_mlp(x, w, w, wd, max_ctas=7)
+    ops.check_status()
+    assert torch.equal(a, b)
+
+
+def test_argument_errors(ops):
+    x = torch.zeros(8, 64, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ValueError):
+        ops.gemm_bf16(x, torch.zeros(8, 32, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(ValueError):
+        ops.gemm_bf16(x.float(), x)
+    with pytest.raises(RuntimeError, match="multiples of 8"):
+        ops.gemm_bf16(x, torch.zeros(12, 64, dtype=torch.bfloat16, device="cuda"))

@@ -240,7 +240,9 @@ def test_tuple_outputs_are_merged_field_by_field():
     x = torch.randn(10, 4)
     host = Host(Two(), cut_policy(r"silu", "act"))
     a, b = host.run((x,), two_way([0, 3, 10]))
-    assert torch.equal(a, F.silu(x) + 1) and torch.equal(b, F.silu(x) * 2)
+    assert a.shape == b.shape == x.shape
+    # (vectorised CPU exp may differ in the last bit between a 12- and a 40-element call)
+    assert torch.allclose(a, F.silu(x) + 1, rtol=1e-6, atol=1e-6) and torch.allclose(b, F.silu(x) * 2, rtol=1e-6, atol=1e-6)
 
 
 # --------------------------------------------------- the CPU parity configuration
