@@ -34,6 +34,7 @@ SIGNATURES: dict[str, tuple] = {
     "df_gateup_silu_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "df_mlp_workspace_bytes": (_sz, [_i, _i, _i]),
     "df_mlp_gated_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "df_mlp_gated_bf16_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
 }
 
 _lib = None

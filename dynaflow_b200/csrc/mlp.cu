@@ -391,3 +391,62 @@ int df_mlp_gated_bf16(const void* x, const void* w_gate, const void* w_up, const
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Variant of df_mlp_gated_bf16 that allocates nothing: the bf16 intermediate
+// lives in a static device array owned by the library.
+//
+// In host code `g_mlp_static_scratch` is only a handle for the runtime's symbol
+// table, not a device address: its device address is looked up per device with
+// cudaGetSymbolAddress (below) and that pointer is what the kernels receive.
+namespace df {
+
+static __device__ __align__(256) unsigned char g_mlp_static_scratch[DF_MLP_STATIC_SCRATCH_BYTES];
+
+constexpr int kMaxDevices = 64;
+static std::mutex g_static_mutex;
+static void* g_static_scratch_ptr[kMaxDevices] = {};
+
+// Device address of the static scratch on the CURRENT device; resolved on the
+// first call for that device and cached. Allocates nothing.
+static int static_scratch_of_current_device(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(DF_ECUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  }
+  if (dev < 0 || dev >= kMaxDevices) return fail(DF_EUNSUPPORTED, "device index %d is outside [0, %d)", dev, kMaxDevices);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_mlp_static_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      (void)cudaGetLastError();
+      return fail(DF_ECUDA, "cudaGetSymbolAddress(static MLP scratch) on device %d: %s", dev, cudaGetErrorString(e));
+    }
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return DF_OK;
+}
+
+}  // namespace df
+
+extern "C" int df_mlp_gated_bf16_static(const void* x, const void* w_gate, const void* w_up, const void* w_down,
+                                        void* out, int M, int H, int I, int max_ctas, df_status_t* dev_status,
+                                        void* stream) {
+  if (M <= 0 || H <= 0 || I <= 0) return df::fail(DF_EINVAL, "M, H, I must be positive (got %d, %d, %d)", M, H, I);
+  const unsigned long long need = 2ull * static_cast<unsigned long long>(M) * static_cast<unsigned long long>(I);
+  if (need > DF_MLP_STATIC_SCRATCH_BYTES)
+    return df::fail(DF_EUNSUPPORTED,
+                    "intermediate of %d x %d bf16 needs %llu bytes, the static scratch holds %u; "
+                    "use df_mlp_gated_bf16 with a caller-owned workspace",
+                    M, I, need, static_cast<unsigned>(DF_MLP_STATIC_SCRATCH_BYTES));
+  void* h = nullptr;
+  int r = df::static_scratch_of_current_device(&h);
+  if (r != DF_OK) return r;
+  r = df_gateup_silu_bf16(x, w_gate, w_up, h, M, H, I, H, H, I, max_ctas, dev_status, stream);
+  if (r != DF_OK) return r;
+  return df_gemm_bf16(h, w_down, out, M, H, I, I, I, H, max_ctas, dev_status, stream);
+}

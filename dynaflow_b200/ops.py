@@ -168,3 +168,35 @@ def gated_mlp(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down:
                                           _stream_ptr(x))
     _check(rc, "df_mlp_gated_bf16")
     return out
+
+
+STATIC_SCRATCH_BYTES = 64 << 20
+
+
+def gated_mlp_static(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
+                     out: torch.Tensor, max_ctas: int = 0) -> torch.Tensor:
+    """``gated_mlp`` for callers that cannot provide or allocate scratch (a policy
+    substitute that only holds the subgraph's tensors, a host whose HBM is fully
+    budgeted): the intermediate lives in a 64 MiB array inside the library, so
+    ``rows * I * 2`` must not exceed ``STATIC_SCRATCH_BYTES`` and ``out`` must be
+    passed in. This wrapper itself creates no tensor. Calls that may overlap on the
+    GPU share that array and race; the first call on a device should happen
+    outside stream capture (it looks up the array's address)."""
+    for name, t in (("x", x), ("w_gate", w_gate), ("w_up", w_up), ("w_down", w_down), ("out", out)):
+        _require_bf16_2d(name, t)
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    M, H = x.shape
+    I = w_gate.shape[0]
+    if tuple(w_gate.shape) != (I, H) or tuple(w_up.shape) != (I, H) or tuple(w_down.shape) != (H, I):
+        raise ValueError("expected w_gate, w_up: [I, H] and w_down: [H, I]")
+    if tuple(out.shape) != (M, H):
+        raise ValueError("out must be [M, H]")
+    if M == 0:
+        return out
+    _dev_index(x)
+    st = status_block(x.device)
+    rc = _native.load().df_mlp_gated_bf16_static(x.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), w_down.data_ptr(),
+                                                 out.data_ptr(), M, H, I, max_ctas, st.data_ptr(), _stream_ptr(x))
+    _check(rc, "df_mlp_gated_bf16_static")
+    return out

@@ -111,6 +111,40 @@ int df_mlp_gated_bf16(const void* x, const void* w_gate, const void* w_up, const
                       void* workspace, int M, int H, int I, int max_ctas, df_status_t* dev_status,
                       void* stream);
 
+/* Size of the library-owned scratch behind df_mlp_gated_bf16_static: 64 MiB of
+ * static device memory, held by every GPU that loads the library until the
+ * process exits. */
+#define DF_MLP_STATIC_SCRATCH_BYTES (64u << 20)
+
+/* Same computation as df_mlp_gated_bf16 for callers that have no scratch to give
+ * and must not allocate any. (No counterpart in the reference: its operators run
+ * inside PyTorch, whose caching allocator provides every temporary.)
+ *
+ * Who needs it: a policy's `func=` substitute is handed only the subgraph's input
+ * tensors, and a serving engine that measured free HBM at start-up and gave the
+ * rest to its KV cache has nothing left to allocate from later; a cudaMalloc in
+ * the middle of a forward would also synchronise the whole device and serialise
+ * the micro-batch streams whose overlap is the point of the schedule. This entry
+ * point therefore keeps the bf16 intermediate h[M,I] in a file-scope __device__
+ * array of DF_MLP_STATIC_SCRATCH_BYTES inside the library and calls no
+ * cudaMalloc, cudaFree or other allocating routine.
+ *
+ * Limits and rules
+ *   - M * I * 2 bytes must fit in DF_MLP_STATIC_SCRATCH_BYTES (e.g. M <= 2340 rows
+ *     at I = 14336); larger shapes are refused with DF_EUNSUPPORTED and a message
+ *     naming both numbers. Use df_mlp_gated_bf16 with your own workspace then.
+ *   - The first call on each device resolves the device address of the array
+ *     (once per device, with that device current). Make that first call outside
+ *     any stream capture.
+ *   - All calls on a device share the one array, and it keeps whatever the last
+ *     call left there; nothing in it has to start at zero (every element that is
+ *     read has been written earlier in the same call). Two calls whose kernels
+ *     can overlap on the GPU (different streams without an ordering between
+ *     them) race on it: order them, or give one of them a workspace of its own
+ *     through df_mlp_gated_bf16. */
+int df_mlp_gated_bf16_static(const void* x, const void* w_gate, const void* w_up, const void* w_down, void* out,
+                             int M, int H, int I, int max_ctas, df_status_t* dev_status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
