@@ -191,8 +191,13 @@ def run_ours(args) -> None:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
+    comm = None
+    if world > 1:
+        from dynaflow_b200.comm import PeerComm
+
+        comm = PeerComm(rank, world, ROWS // MICRO_BATCHES, H, slots=MICRO_BATCHES, n_ctas=args.comm_ctas, device=dev)
     layer = TensorParallelGatedMLP(H, I, rank=rank, world=world, max_rows=ROWS // MICRO_BATCHES,
-                                   micro_batches=MICRO_BATCHES, seed=0, device=dev)
+                                   micro_batches=MICRO_BATCHES, seed=0, device=dev, comm=comm)
     gen = torch.Generator().manual_seed(1)
     x_host = torch.randn(ROWS, H, generator=gen).bfloat16().pin_memory()
     out_host = torch.empty(ROWS, H, dtype=torch.bfloat16).pin_memory()
@@ -307,6 +312,7 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--rows", type=int, default=ROWS, help="rows per step (default: the benchmark's 16384; "
                     "smaller values are for profiler captures only)")
+    ap.add_argument("--comm-ctas", type=int, default=32, help="CTAs of the peer-memory all-reduce kernel (N > 1)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     args = ap.parse_args()
     if args.rows != ROWS:

@@ -22,6 +22,19 @@ class df_status_t(ctypes.Structure):
 
 _vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
 
+MAX_WORLD = 8
+MAX_CTAS = 64
+
+
+class df_comm_rank_t(ctypes.Structure):
+    _fields_ = [("rank", ctypes.c_int), ("regions", ctypes.c_void_p * MAX_WORLD),
+                ("residual_in", ctypes.c_void_p), ("residual_out", ctypes.c_void_p), ("out", ctypes.c_void_p)]
+
+
+_handle = ctypes.c_ubyte * 64
+_f = ctypes.c_float
+_rank_p = ctypes.POINTER(df_comm_rank_t)
+
 # name -> (restype, argtypes); must list every symbol the public header declares
 SIGNATURES: dict[str, tuple] = {
     "df_version": (_i, []),
@@ -34,6 +47,16 @@ SIGNATURES: dict[str, tuple] = {
     "df_gateup_silu_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "df_mlp_workspace_bytes": (_sz, [_i, _i, _i]),
     "df_mlp_gated_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "df_comm_region_bytes": (_sz, [_i, _i]),
+    "df_comm_partial_offset": (_sz, [_i, _i]),
+    "df_comm_sum_offset": (_sz, [_i, _i]),
+    "df_comm_region_alloc": (_i, [_sz, ctypes.POINTER(_vp), ctypes.POINTER(_handle)]),
+    "df_comm_region_open": (_i, [ctypes.POINTER(_handle), ctypes.POINTER(_vp)]),
+    "df_comm_region_close": (_i, [_vp]),
+    "df_comm_region_free": (_i, [_vp]),
+    "df_allreduce_bf16": (_i, [_rank_p, _i, _i, _i, _i, _i, _vp, _vp]),
+    "df_allreduce_add_rmsnorm_bf16": (_i, [_rank_p, _i, _i, _i, _i, _vp, _f, _i, _vp, _vp]),
+    "df_allreduce_emulated_bf16": (_i, [_rank_p, _i, _i, _i, _i, _vp, _f, _i, _i, _vp, _vp]),
     "df_mlp_gated_bf16_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
 }
 

@@ -1,0 +1,193 @@
+"""Peer-memory communicator for the tensor-parallel reduction of a micro-batch.
+
+``PeerComm`` is the multi-process form (one process per GPU): every rank allocates
+one region per micro-batch slot through the C ABI, the 64-byte CUDA IPC handles are
+exchanged with ``torch.distributed.all_gather_object`` (plumbing only), and each
+rank maps its peers' regions. ``EmulatedComm`` keeps all ranks' regions on one GPU
+and runs them as one cooperative launch (tests without a second GPU).
+
+The all-reduce replaces the ``network``-tagged all-reduce (+ RMSNorm) subgraph of a
+TP model (``examples/ae/scheduler/vllm/nanoflow.py:59-69, 171-211``); a policy
+substitutes it with ``PeerComm.all_reduce`` / ``all_reduce_add_rmsnorm`` on its
+communication stream.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Any
+
+import torch
+
+from . import _native, ops
+from ._native import df_comm_rank_t
+
+
+class _DevicePointer:
+    """Adapter exposing raw device memory to torch through ``__cuda_array_interface__``."""
+
+    def __init__(self, ptr: int, nbytes: int) -> None:
+        self.__cuda_array_interface__ = {"shape": (nbytes // 2,), "typestr": "<i2", "data": (ptr, False),
+                                         "version": 2}
+
+
+def _bf16_view(ptr: int, rows: int, hidden: int, device: torch.device) -> torch.Tensor:
+    t = torch.as_tensor(_DevicePointer(ptr, rows * hidden * 2), device=device)
+    return t.view(torch.bfloat16).view(rows, hidden)
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed ({rc}): {_native.last_error()}")
+
+
+class _Regions:
+    """Layout bookkeeping shared by the two communicators."""
+
+    def __init__(self, world: int, max_rows: int, hidden: int, slots: int, n_ctas: int, device: torch.device) -> None:
+        if not 1 <= world <= _native.MAX_WORLD:
+            raise ValueError(f"world size {world} is outside [1, {_native.MAX_WORLD}]")
+        if hidden % 8 != 0:
+            raise ValueError("hidden must be a multiple of 8")
+        self.lib = _native.load()
+        self.world, self.max_rows, self.hidden, self.slots = world, max_rows, hidden, slots
+        self.n_ctas = n_ctas
+        self.device = device
+        self.region_bytes = int(self.lib.df_comm_region_bytes(max_rows, hidden))
+        self.partial_off = int(self.lib.df_comm_partial_offset(max_rows, hidden))
+        self.sum_off = int(self.lib.df_comm_sum_offset(max_rows, hidden))
+        self.launches = 0
+        self.bytes_reduced = 0
+
+    def _view(self, rank: int, regions: list[int], residual_in=None, residual_out=None, out=None) -> df_comm_rank_t:
+        v = df_comm_rank_t()
+        v.rank = rank
+        for r, ptr in enumerate(regions):
+            v.regions[r] = ptr
+        v.residual_in = residual_in.data_ptr() if residual_in is not None else None
+        v.residual_out = residual_out.data_ptr() if residual_out is not None else None
+        v.out = out.data_ptr() if out is not None else None
+        return v
+
+
+class PeerComm(_Regions):
+    def __init__(self, rank: int, world: int, max_rows: int, hidden: int, *, slots: int = 2, n_ctas: int = 32,
+                 device: torch.device | None = None, group: Any = None) -> None:
+        import torch.distributed as dist
+
+        device = device or torch.device("cuda", torch.cuda.current_device())
+        super().__init__(world, max_rows, hidden, slots, n_ctas, device)
+        self.rank = rank
+        self.local: list[int] = []
+        handles: list[bytes] = []
+        with torch.cuda.device(device):
+            for _ in range(slots):
+                ptr = ctypes.c_void_p()
+                handle = (ctypes.c_ubyte * 64)()
+                _check(self.lib.df_comm_region_alloc(self.region_bytes, ctypes.byref(ptr), ctypes.byref(handle)),
+                       "df_comm_region_alloc")
+                self.local.append(ptr.value)
+                handles.append(bytes(handle))
+        gathered: list[Any] = [None] * world
+        if world > 1:
+            dist.all_gather_object(gathered, handles, group=group)
+        else:
+            gathered[0] = handles
+        # regions[slot][r] = rank r's region for that slot, as mapped in this process
+        self.regions: list[list[int]] = []
+        self._opened: list[int] = []
+        with torch.cuda.device(device):
+            for slot in range(slots):
+                row = []
+                for r in range(world):
+                    if r == rank:
+                        row.append(self.local[slot])
+                        continue
+                    ptr = ctypes.c_void_p()
+                    handle = (ctypes.c_ubyte * 64).from_buffer_copy(gathered[r][slot])
+                    _check(self.lib.df_comm_region_open(ctypes.byref(handle), ctypes.byref(ptr)), "df_comm_region_open")
+                    row.append(ptr.value)
+                    self._opened.append(ptr.value)
+                self.regions.append(row)
+        if world > 1:
+            dist.barrier(group=group)  # every rank has mapped every region before anyone launches
+        self._partials = [_bf16_view(self.local[s] + self.partial_off, max_rows, hidden, device) for s in range(slots)]
+        self._sums = [_bf16_view(self.local[s] + self.sum_off, max_rows, hidden, device) for s in range(slots)]
+        self.stream = torch.cuda.Stream(device=device)
+
+    def partial(self, slot: int, rows: int) -> torch.Tensor:
+        """Where this rank's partial sums of micro-batch slot ``slot`` must be written."""
+        return self._partials[slot][:rows]
+
+    def result(self, slot: int, rows: int) -> torch.Tensor:
+        """The reduced rows after ``all_reduce`` (identical on every rank)."""
+        return self._sums[slot][:rows]
+
+    def all_reduce(self, slot: int, rows: int) -> torch.Tensor:
+        """Launches on the current stream; returns ``result(slot, rows)``."""
+        view = self._view(self.rank, self.regions[slot])
+        st = ops.status_block(self.device)
+        _check(self.lib.df_allreduce_bf16(ctypes.byref(view), self.world, self.max_rows, self.hidden, rows, self.n_ctas,
+                                          st.data_ptr(), torch.cuda.current_stream(self.device).cuda_stream),
+               "df_allreduce_bf16")
+        self.launches += 1
+        self.bytes_reduced += rows * self.hidden * 2
+        return self.result(slot, rows)
+
+    def all_reduce_add_rmsnorm(self, slot: int, rows: int, residual: torch.Tensor | None, weight: torch.Tensor,
+                               out: torch.Tensor, residual_out: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+        view = self._view(self.rank, self.regions[slot], residual, residual_out, out)
+        st = ops.status_block(self.device)
+        _check(self.lib.df_allreduce_add_rmsnorm_bf16(ctypes.byref(view), self.world, self.max_rows, self.hidden, rows,
+                                                      weight.data_ptr(), eps, self.n_ctas, st.data_ptr(),
+                                                      torch.cuda.current_stream(self.device).cuda_stream),
+               "df_allreduce_add_rmsnorm_bf16")
+        self.launches += 1
+        self.bytes_reduced += rows * self.hidden * 2
+        return out
+
+    def summary(self) -> dict:
+        return {"kind": "peer-memory two-shot all-reduce (hand-written, no NCCL on the data path)",
+                "n_ctas": self.n_ctas, "launches": self.launches, "payload_bytes": self.bytes_reduced}
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.device)
+        self._partials, self._sums = [], []
+        with torch.cuda.device(self.device):
+            for ptr in self._opened:
+                self.lib.df_comm_region_close(ptr)
+            for ptr in self.local:
+                self.lib.df_comm_region_free(ptr)
+        self._opened, self.local = [], []
+
+
+class EmulatedComm(_Regions):
+    """All ranks on one GPU, one cooperative launch (grid.y = rank)."""
+
+    def __init__(self, world: int, max_rows: int, hidden: int, n_ctas: int = 8, device: torch.device | None = None) -> None:
+        device = device or torch.device("cuda", torch.cuda.current_device())
+        super().__init__(world, max_rows, hidden, 1, n_ctas, device)
+        self.buffers = [torch.zeros(self.region_bytes, dtype=torch.uint8, device=device) for _ in range(world)]
+        self.ptrs = [b.data_ptr() for b in self.buffers]
+
+    def partial(self, rank: int, rows: int) -> torch.Tensor:
+        b = self.buffers[rank][self.partial_off:self.partial_off + self.max_rows * self.hidden * 2]
+        return b.view(torch.bfloat16).view(self.max_rows, self.hidden)[:rows]
+
+    def result(self, rank: int, rows: int) -> torch.Tensor:
+        b = self.buffers[rank][self.sum_off:self.sum_off + self.max_rows * self.hidden * 2]
+        return b.view(torch.bfloat16).view(self.max_rows, self.hidden)[:rows]
+
+    def run(self, rows: int, *, weight: torch.Tensor | None = None, residual_in: list | None = None,
+            residual_out: list | None = None, out: list | None = None, eps: float = 1e-5) -> None:
+        fuse = weight is not None
+        views = (df_comm_rank_t * self.world)()
+        for r in range(self.world):
+            v = self._view(r, self.ptrs, residual_in[r] if (fuse and residual_in) else None,
+                           residual_out[r] if fuse else None, out[r] if fuse else None)
+            views[r] = v
+        st = ops.status_block(self.device)
+        _check(self.lib.df_allreduce_emulated_bf16(views, self.world, self.max_rows, self.hidden, rows,
+                                                   weight.data_ptr() if fuse else None, eps, 1 if fuse else 0,
+                                                   self.n_ctas, st.data_ptr(),
+                                                   torch.cuda.current_stream(self.device).cuda_stream),
+               "df_allreduce_emulated_bf16")

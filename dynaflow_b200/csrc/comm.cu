@@ -1,0 +1,421 @@
+// Tensor-parallel reduction of one micro-batch over NVLink peer memory:
+// two-shot all-reduce (reduce-scatter by row slices, then all-gather by peer
+// stores) with an optional fused residual-add + RMSNorm epilogue.
+//
+// Every rank owns a "region" of device memory that all ranks have mapped
+// (CUDA IPC): a partial-sum buffer the rank's down projection writes into, a
+// sum buffer its peers push reduced rows into, and flag words. One launch:
+//
+//   barrier 0   block b of every rank tells block b of every peer that the
+//               rank's partial buffer is complete
+//   phase 1     rank r reduces the rows of slice r: a warp loads one row from
+//               all W partial buffers (16-byte peer loads), adds in fp32 in
+//               rank order, rounds to bf16 and stores the row into the sum
+//               buffer of all W ranks (peer stores)
+//   barrier 1   block b of every rank has pushed its rows
+//   phase 2     local: the rows that the blocks b delivered are finished on
+//               this rank -- nothing (the result is the sum buffer), or
+//               r' = y + residual; out = rmsnorm(r') * w
+//
+// Blocks only ever synchronise with the same-index block of the other ranks,
+// and block b consumes in phase 2 exactly the rows that the blocks b produced,
+// so there is no grid-wide barrier. Flags carry a per-block sequence number
+// kept in device memory, which makes the kernel replayable from a CUDA graph.
+// Waits are bounded by the library deadline; a peer that never shows up yields
+// DF_ERR_PEER in the status block and the kernel returns.
+//
+// No multimem / NVLS and no TMA are used here: plain ld/st.global on peer
+// pointers through NVSwitch.
+#include <cooperative_groups.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstring>
+
+#include "../../include/dynaflow_b200.h"
+#include "host_util.h"
+#include "ptx.cuh"
+
+namespace df {
+
+constexpr int kMaxWorld = DF_COMM_MAX_WORLD;
+// 256 threads at <= 104 registers: a CTA of this kernel fits on an SM beside a
+// resident GEMM CTA (256 threads x 96 registers, 197 KB shared memory), so the
+// reduction does not have to wait for the persistent GEMM to leave.
+constexpr int kCommThreads = 256;
+constexpr int kWarpsPerBlock = kCommThreads / 32;
+constexpr int kMaxCtas = DF_COMM_MAX_CTAS;
+constexpr unsigned WHERE_FLAG = 16;
+
+// Layout of a region (all offsets multiples of 256 bytes):
+//   [0, 4096)                         flag words: uint32 flags[2][kMaxCtas][kMaxWorld]
+//   [4096, 4096 + 4*kMaxCtas)         block sequence numbers
+//   partial buffer  max_rows x hidden bf16
+//   sum buffer      max_rows x hidden bf16
+constexpr size_t kFlagBytes = 2ull * kMaxCtas * kMaxWorld * 4;  // 4096 with 64 CTAs x 8 ranks
+constexpr size_t kSeqOffset = kFlagBytes;
+constexpr size_t kHeaderBytes = 8192;
+
+static size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+
+struct RankView {
+  int rank;
+  const __nv_bfloat16* partial[kMaxWorld];
+  __nv_bfloat16* sum[kMaxWorld];
+  uint32_t* flags[kMaxWorld];
+  uint32_t* seq;               // this rank's per-block sequence numbers
+  const __nv_bfloat16* residual_in;
+  __nv_bfloat16* residual_out;
+  __nv_bfloat16* out;
+};
+
+struct CommParams {
+  RankView ranks[kMaxWorld];   // [0] only, unless several ranks are emulated on one GPU
+  const __nv_bfloat16* weight;
+  int world, T, H, mode;
+  float eps;
+  unsigned long long timeout_ns;
+  Status* status;
+};
+
+enum : int { EPI_NONE = 0, EPI_ADD_RMSNORM = 1 };
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Block-level barrier with the same-index block of every peer. Thread t < world
+// signals peer t and then waits for peer t's signal. Returns false (for the
+// whole block) if a wait ran out.
+__device__ __forceinline__ bool peer_barrier(const RankView& me, int world, int phase, uint32_t seq,
+                                             unsigned long long t_end, Status* status, uint32_t* s_abort) {
+  __syncthreads();  // all of this block's earlier stores are ordered before the signal
+  const int t = threadIdx.x;
+  if (t < world) {
+    const uint32_t value = seq * 2u + static_cast<uint32_t>(phase) + 1u;
+    const size_t slot = (static_cast<size_t>(phase) * kMaxCtas + blockIdx.x) * kMaxWorld;
+    __threadfence_system();
+    st_release_sys(me.flags[t] + slot + me.rank, value);
+    const uint32_t* mine = me.flags[me.rank] + slot + t;
+    uint32_t spins = 0;
+    // flags only grow; compare as a signed distance so that wrap-around is harmless
+    while (static_cast<int32_t>(ld_acquire_sys(mine) - value) < 0) {
+      if ((++spins & 0xffu) == 0u && globaltimer_ns() > t_end) {
+        *s_abort = 1u;
+        report(status, 2u /*DF_ERR_PEER*/, WHERE_FLAG + phase, static_cast<unsigned>(t));
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return *s_abort == 0u;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x = __bfloat1622float2(h[i]);
+    f[2 * i] = x.x;
+    f[2 * i + 1] = x.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+
+template <int W, bool EMULATE>
+__global__ void __launch_bounds__(kCommThreads, 2) allreduce_kernel(const CommParams p) {
+  __shared__ uint32_t s_abort;
+  const RankView& me = p.ranks[EMULATE ? blockIdx.y : 0];
+  if (threadIdx.x == 0) s_abort = 0u;
+  const unsigned long long t_end = globaltimer_ns() + p.timeout_ns;
+  const uint32_t seq = me.seq[blockIdx.x];  // same value on every rank: one increment per launch
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = p.H >> 3;
+  const int row_stride = gridDim.x * kWarpsPerBlock;
+  const int row_first = blockIdx.x * kWarpsPerBlock + warp;
+
+  bool ok = peer_barrier(me, W, 0, seq, t_end, p.status, &s_abort);
+
+  if (ok) {
+    // ---- phase 1: reduce this rank's slice and push it to everyone
+    const int lo = static_cast<int>(static_cast<long long>(p.T) * me.rank / W);
+    const int hi = static_cast<int>(static_cast<long long>(p.T) * (me.rank + 1) / W);
+    for (int row = lo + row_first; row < hi; row += row_stride) {
+      const size_t base = static_cast<size_t>(row) * p.H;
+      for (int v0 = lane; v0 < nvec; v0 += 64) {
+        const int v1 = v0 + 32;
+        const bool two = v1 < nvec;
+        uint4 a[W], b[W];
+#pragma unroll
+        for (int r = 0; r < W; ++r) {
+          a[r] = __ldcg(reinterpret_cast<const uint4*>(me.partial[r] + base) + v0);
+          if (two) b[r] = __ldcg(reinterpret_cast<const uint4*>(me.partial[r] + base) + v1);
+        }
+        float sa[8] = {0, 0, 0, 0, 0, 0, 0, 0}, sb[8] = {0, 0, 0, 0, 0, 0, 0, 0}, f[8];
+#pragma unroll
+        for (int r = 0; r < W; ++r) {
+          unpack8(a[r], f);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sa[i] += f[i];
+          if (two) {
+            unpack8(b[r], f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sb[i] += f[i];
+          }
+        }
+        const uint4 ya = pack8(sa), yb = pack8(sb);
+#pragma unroll
+        for (int r = 0; r < W; ++r) {
+          __stcg(reinterpret_cast<uint4*>(me.sum[r] + base) + v0, ya);
+          if (two) __stcg(reinterpret_cast<uint4*>(me.sum[r] + base) + v1, yb);
+        }
+      }
+    }
+    ok = peer_barrier(me, W, 1, seq, t_end, p.status, &s_abort);
+  }
+
+  if (ok && p.mode == EPI_ADD_RMSNORM) {
+    // ---- phase 2: residual add + RMSNorm of the rows the blocks with this index delivered
+    const float inv_h = 1.0f / static_cast<float>(p.H);
+    for (int q = 0; q < W; ++q) {
+      const int lo = static_cast<int>(static_cast<long long>(p.T) * q / W);
+      const int hi = static_cast<int>(static_cast<long long>(p.T) * (q + 1) / W);
+      for (int row = lo + row_first; row < hi; row += row_stride) {
+        const size_t base = static_cast<size_t>(row) * p.H;
+        const uint4* y = reinterpret_cast<const uint4*>(me.sum[me.rank] + base);
+        uint4* res_out = reinterpret_cast<uint4*>(me.residual_out + base);
+        float ss = 0.0f;
+        for (int v = lane; v < nvec; v += 32) {
+          float fy[8], fr[8];
+          unpack8(__ldcg(y + v), fy);
+          if (me.residual_in != nullptr) {
+            unpack8(reinterpret_cast<const uint4*>(me.residual_in + base)[v], fr);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) fy[i] += fr[i];
+          }
+          const uint4 packed = pack8(fy);
+          res_out[v] = packed;
+          unpack8(packed, fy);  // the sum of squares is taken over the rounded residual
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ss += fy[i] * fy[i];
+        }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        const float inv = rsqrtf(ss * inv_h + p.eps);
+        uint4* o = reinterpret_cast<uint4*>(me.out + base);
+        for (int v = lane; v < nvec; v += 32) {
+          float fx[8], fw[8];
+          unpack8(res_out[v], fx);
+          unpack8(reinterpret_cast<const uint4*>(p.weight)[v], fw);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) fx[i] = __bfloat162float(__float2bfloat16_rn(fx[i] * inv)) * fw[i];
+          o[v] = pack8(fx);
+        }
+      }
+    }
+  }
+
+  __syncthreads();
+  if (threadIdx.x == 0) me.seq[blockIdx.x] = seq + 1u;  // also after a failed wait: the ranks stay in step
+}
+
+// ------------------------------------------------------------------- host
+
+struct RegionLayout {
+  size_t partial_off, sum_off, total;
+};
+
+static RegionLayout region_layout(int max_rows, int hidden) {
+  RegionLayout l;
+  const size_t buf = align256(static_cast<size_t>(max_rows) * static_cast<size_t>(hidden) * 2u);
+  l.partial_off = kHeaderBytes;
+  l.sum_off = l.partial_off + buf;
+  l.total = l.sum_off + buf;
+  return l;
+}
+
+template <bool EMULATE>
+static int launch_allreduce(const CommParams& p, int n_ctas, int emulated, void* stream) {
+  dim3 grid(n_ctas, EMULATE ? emulated : 1, 1);
+  dim3 block(kCommThreads, 1, 1);
+  void* args[] = {const_cast<CommParams*>(&p)};
+  const void* fn = nullptr;
+  switch (p.world) {
+#define DF_CASE(W)                                                          \
+  case W:                                                                   \
+    fn = reinterpret_cast<const void*>(&allreduce_kernel<W, EMULATE>);      \
+    break;
+    DF_CASE(1) DF_CASE(2) DF_CASE(3) DF_CASE(4) DF_CASE(5) DF_CASE(6) DF_CASE(7) DF_CASE(8)
+#undef DF_CASE
+    default:
+      return fail(DF_EUNSUPPORTED, "world size %d is outside [1, %d]", p.world, kMaxWorld);
+  }
+  cudaError_t e;
+  if (EMULATE) {
+    // every emulated rank must be resident at once: its blocks wait on the others'
+    e = cudaLaunchCooperativeKernel(fn, grid, block, args, 0, static_cast<cudaStream_t>(stream));
+  } else {
+    e = cudaLaunchKernel(fn, grid, block, args, 0, static_cast<cudaStream_t>(stream));
+  }
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(DF_ECUDA, "all-reduce launch: %s", cudaGetErrorString(e));
+  }
+  return DF_OK;
+}
+
+static int fill_params(CommParams* p, int n_views, const df_comm_rank_t* views, int world, int max_rows, int hidden,
+                       int T, int H, int mode, const void* weight, float eps, df_status_t* dev_status) {
+  if (views == nullptr || dev_status == nullptr) return fail(DF_EINVAL, "NULL pointer argument");
+  if (world < 1 || world > kMaxWorld) return fail(DF_EUNSUPPORTED, "world size %d is outside [1, %d]", world, kMaxWorld);
+  if (T <= 0 || H <= 0 || (H % 8) != 0) return fail(DF_EINVAL, "T must be positive and H a positive multiple of 8");
+  if (H != hidden || T > max_rows)
+    return fail(DF_EINVAL, "T=%d, H=%d do not fit the region (max_rows=%d, hidden=%d)", T, H, max_rows, hidden);
+  if (mode == EPI_ADD_RMSNORM && weight == nullptr) return fail(DF_EINVAL, "RMSNorm weight is NULL");
+  const RegionLayout l = region_layout(max_rows, hidden);
+  std::memset(p, 0, sizeof(*p));
+  for (int v = 0; v < n_views; ++v) {
+    const df_comm_rank_t& in = views[v];
+    RankView& out = p->ranks[v];
+    if (in.rank < 0 || in.rank >= world) return fail(DF_EINVAL, "rank %d is outside [0, %d)", in.rank, world);
+    out.rank = in.rank;
+    for (int r = 0; r < world; ++r) {
+      uint8_t* region = static_cast<uint8_t*>(in.regions[r]);
+      if (region == nullptr || (reinterpret_cast<uintptr_t>(region) & 255u) != 0)
+        return fail(DF_EINVAL, "region pointer of rank %d is NULL or not 256-byte aligned", r);
+      out.partial[r] = reinterpret_cast<const __nv_bfloat16*>(region + l.partial_off);
+      out.sum[r] = reinterpret_cast<__nv_bfloat16*>(region + l.sum_off);
+      out.flags[r] = reinterpret_cast<uint32_t*>(region);
+    }
+    out.seq = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(in.regions[in.rank]) + kSeqOffset);
+    out.residual_in = static_cast<const __nv_bfloat16*>(in.residual_in);
+    out.residual_out = static_cast<__nv_bfloat16*>(in.residual_out);
+    out.out = static_cast<__nv_bfloat16*>(in.out);
+    if (mode == EPI_ADD_RMSNORM) {
+      if (in.residual_out == nullptr || in.out == nullptr) return fail(DF_EINVAL, "residual_out / out is NULL");
+      if ((reinterpret_cast<uintptr_t>(in.residual_out) & 15u) || (reinterpret_cast<uintptr_t>(in.out) & 15u) ||
+          (reinterpret_cast<uintptr_t>(in.residual_in) & 15u) || (reinterpret_cast<uintptr_t>(weight) & 15u))
+        return fail(DF_EINVAL, "residual, out and weight pointers must be 16-byte aligned");
+    }
+  }
+  p->weight = static_cast<const __nv_bfloat16*>(weight);
+  p->world = world;
+  p->T = T;
+  p->H = H;
+  p->mode = mode;
+  p->eps = eps;
+  p->timeout_ns = timeout_ns();
+  p->status = reinterpret_cast<Status*>(dev_status);
+  return DF_OK;
+}
+
+static int clamp_ctas(int n_ctas) {
+  if (n_ctas <= 0) n_ctas = 32;
+  return n_ctas > kMaxCtas ? kMaxCtas : n_ctas;
+}
+
+}  // namespace df
+
+extern "C" {
+
+size_t df_comm_region_bytes(int max_rows, int hidden) {
+  if (max_rows <= 0 || hidden <= 0 || (hidden % 8) != 0) return 0;
+  return df::region_layout(max_rows, hidden).total;
+}
+
+size_t df_comm_partial_offset(int max_rows, int hidden) { return df::region_layout(max_rows, hidden).partial_off; }
+
+size_t df_comm_sum_offset(int max_rows, int hidden) { return df::region_layout(max_rows, hidden).sum_off; }
+
+int df_comm_region_alloc(size_t bytes, void** dev_ptr, unsigned char ipc_handle[64]) {
+  if (dev_ptr == nullptr || bytes < df::kHeaderBytes) return df::fail(DF_EINVAL, "bad region size or NULL output pointer");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e == cudaSuccess) e = cudaMemset(p, 0, df::kHeaderBytes);  // flags and sequence numbers start at zero
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e == cudaSuccess && ipc_handle != nullptr) {
+    cudaIpcMemHandle_t h;
+    e = cudaIpcGetMemHandle(&h, p);
+    if (e == cudaSuccess) std::memcpy(ipc_handle, &h, 64);
+  }
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    if (p != nullptr) cudaFree(p);
+    return df::fail(DF_ECUDA, "region alloc: %s", cudaGetErrorString(e));
+  }
+  *dev_ptr = p;
+  return DF_OK;
+}
+
+int df_comm_region_open(const unsigned char ipc_handle[64], void** dev_ptr) {
+  if (ipc_handle == nullptr || dev_ptr == nullptr) return df::fail(DF_EINVAL, "NULL pointer argument");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, ipc_handle, 64);
+  cudaError_t e = cudaIpcOpenMemHandle(dev_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return df::fail(DF_ECUDA, "cudaIpcOpenMemHandle: %s", cudaGetErrorString(e));
+  }
+  return DF_OK;
+}
+
+int df_comm_region_close(void* peer_ptr) {
+  cudaError_t e = cudaIpcCloseMemHandle(peer_ptr);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return df::fail(DF_ECUDA, "cudaIpcCloseMemHandle: %s", cudaGetErrorString(e));
+  }
+  return DF_OK;
+}
+
+int df_comm_region_free(void* dev_ptr) {
+  cudaError_t e = cudaFree(dev_ptr);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return df::fail(DF_ECUDA, "cudaFree: %s", cudaGetErrorString(e));
+  }
+  return DF_OK;
+}
+
+int df_allreduce_bf16(const df_comm_rank_t* view, int world, int max_rows, int hidden, int T, int n_ctas,
+                      df_status_t* dev_status, void* stream) {
+  df::CommParams p;
+  int r = df::fill_params(&p, 1, view, world, max_rows, hidden, T, hidden, df::EPI_NONE, nullptr, 0.0f, dev_status);
+  if (r != DF_OK) return r;
+  return df::launch_allreduce<false>(p, df::clamp_ctas(n_ctas), 1, stream);
+}
+
+int df_allreduce_add_rmsnorm_bf16(const df_comm_rank_t* view, int world, int max_rows, int hidden, int T,
+                                  const void* weight, float eps, int n_ctas, df_status_t* dev_status, void* stream) {
+  df::CommParams p;
+  int r = df::fill_params(&p, 1, view, world, max_rows, hidden, T, hidden, df::EPI_ADD_RMSNORM, weight, eps, dev_status);
+  if (r != DF_OK) return r;
+  return df::launch_allreduce<false>(p, df::clamp_ctas(n_ctas), 1, stream);
+}
+
+int df_allreduce_emulated_bf16(const df_comm_rank_t* views, int world, int max_rows, int hidden, int T,
+                               const void* weight, float eps, int fuse_rmsnorm, int n_ctas, df_status_t* dev_status,
+                               void* stream) {
+  df::CommParams p;
+  int r = df::fill_params(&p, world, views, world, max_rows, hidden, T, hidden,
+                          fuse_rmsnorm ? df::EPI_ADD_RMSNORM : df::EPI_NONE, weight, eps, dev_status);
+  if (r != DF_OK) return r;
+  for (int v = 0; v < world; ++v)
+    if (views[v].rank != v) return df::fail(DF_EINVAL, "emulated views must be listed in rank order");
+  return df::launch_allreduce<true>(p, df::clamp_ctas(n_ctas), world, stream);
+}
+
+}  // extern "C"

@@ -36,8 +36,8 @@ class TensorParallelGatedMLP:
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.micro_batches = micro_batches
         self.max_rows = max_rows
-        shard = intermediate // world
-        lo, hi = rank * shard, (rank + 1) * shard
+        lo, hi = shard_bounds(intermediate, rank, world)
+        shard = hi - lo
         if weights is None:
             # full weights N(0, 0.02) from the seed (identical on every rank), then this rank's shard
             g = torch.Generator().manual_seed(seed)
@@ -80,24 +80,43 @@ class TensorParallelGatedMLP:
             ops.gated_mlp(x, self.w_gate, self.w_up, self.w_down, out=out, workspace=self.workspaces[mb])
         return marks
 
-    def forward_device(self, x: torch.Tensor, out: torch.Tensor, cuts: list[int], record_kernel_events: bool = False):
-        """``out[cuts[i]:cuts[i+1]] = mlp(x[cuts[i]:cuts[i+1]])`` for every micro-batch ``i``."""
+    def forward_device(self, x: torch.Tensor, out: torch.Tensor, cuts: list[int], record_kernel_events: bool = False,
+                       results: list | None = None):
+        """Runs ``mlp(x[cuts[i]:cuts[i+1]])`` for every micro-batch ``i`` on the current stream.
+
+        Single rank: the rows land in ``out``. Tensor parallel: each micro-batch's partial
+        output is written straight into the communicator's region and reduced on the
+        communication stream while the next micro-batch's GEMMs run; the reduced rows
+        are then ``comm.result(slot, rows)`` (appended to ``results`` if given), and the
+        current stream waits for the last reduction before the call returns."""
         marks = []
+        main = torch.cuda.current_stream(self.device)
         for mb in range(len(cuts) - 1):
             lo, hi = cuts[mb], cuts[mb + 1]
             if hi == lo:
                 continue
-            m = self._mlp(x[lo:hi], out[lo:hi], mb % self.micro_batches, record_kernel_events)
-            if self.world > 1:
-                self.comm.all_reduce_async(out[lo:hi], mb)
+            slot = mb % self.micro_batches
+            target = out[lo:hi] if self.world == 1 else self.comm.partial(slot, hi - lo)
+            m = self._mlp(x[lo:hi], target, slot, record_kernel_events)
             if m is not None:
                 marks.append(m)
+            if self.world > 1:
+                ready = torch.cuda.Event()
+                ready.record(main)
+                self.comm.stream.wait_event(ready)
+                with torch.cuda.stream(self.comm.stream):
+                    reduced = self.comm.all_reduce(slot, hi - lo)
+                if results is not None:
+                    results.append(reduced)
+            elif results is not None:
+                results.append(target)
         if self.world > 1:
-            self.comm.join()
+            main.wait_stream(self.comm.stream)
         return marks
 
     def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, cuts: list[int]) -> None:
-        """Same step from pinned host memory; copies ride on the micro-batch's own stream."""
+        """Same step from pinned host memory: copy-in, GEMMs, reduction and copy-out of a
+        micro-batch ride on that micro-batch's own stream."""
         main = torch.cuda.current_stream(self.device)
         fork = torch.cuda.Event()
         fork.record(main)
@@ -111,11 +130,23 @@ class TensorParallelGatedMLP:
             stream.wait_event(fork)
             with torch.cuda.stream(stream):
                 xin = self.staging_in[slot][: hi - lo]
-                yout = self.staging_out[slot][: hi - lo]
                 xin.copy_(x_host[lo:hi], non_blocking=True)
-                self._mlp(xin, yout, slot, False)
-                if self.world > 1:
-                    self.comm.all_reduce_on_current_stream(yout, slot)
+                if self.world == 1:
+                    yout = self.staging_out[slot][: hi - lo]
+                    self._mlp(xin, yout, slot, False)
+                else:
+                    self._mlp(xin, self.comm.partial(slot, hi - lo), slot, False)
+                    # reductions of all micro-batches go through the ONE communication stream, so
+                    # every rank issues them in the same order and two of them never wait on each
+                    # other across GPUs in opposite orders
+                    ready = torch.cuda.Event()
+                    ready.record(stream)
+                    self.comm.stream.wait_event(ready)
+                    with torch.cuda.stream(self.comm.stream):
+                        yout = self.comm.all_reduce(slot, hi - lo)
+                        reduced = torch.cuda.Event()
+                        reduced.record(self.comm.stream)
+                    stream.wait_event(reduced)
                 out_host[lo:hi].copy_(yout, non_blocking=True)
                 done = torch.cuda.Event()
                 done.record(stream)
@@ -125,3 +156,11 @@ class TensorParallelGatedMLP:
 
     def comm_summary(self) -> dict:
         return self.comm.summary() if self.comm is not None else {}
+
+
+def shard_bounds(intermediate: int, rank: int, world: int) -> tuple[int, int]:
+    """Rows of W_gate / W_up (columns of W_down) that rank ``rank`` of ``world`` owns."""
+    if intermediate % world != 0:
+        raise ValueError("the intermediate size must divide evenly across ranks")
+    shard = intermediate // world
+    return rank * shard, (rank + 1) * shard

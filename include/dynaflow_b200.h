@@ -10,8 +10,8 @@
  *     (df_last_error() has the text); device-side failures (a bounded wait
  *     that ran out) are reported asynchronously in the df_status_t block the
  *     caller passed, never by trapping or spinning forever;
- *   - no entry point allocates or frees device memory, none synchronises the
- *     host with the device unless its comment says so;
+ *   - no entry point allocates or frees device memory and none synchronises the
+ *     host with the device, unless its comment says so (df_comm_region_* do);
  *   - bf16 matrices are row-major with an explicit leading dimension counted
  *     in elements; all base pointers 16-byte aligned, leading dimensions a
  *     multiple of 8 elements.
@@ -110,6 +110,71 @@ size_t df_mlp_workspace_bytes(int M, int H, int I);
 int df_mlp_gated_bf16(const void* x, const void* w_gate, const void* w_up, const void* w_down, void* out,
                       void* workspace, int M, int H, int I, int max_ctas, df_status_t* dev_status,
                       void* stream);
+
+/* ------------------------------------------- tensor-parallel reduction
+ *
+ * Replaces the all-reduce (+ residual add + RMSNorm) subgraph that a policy tags
+ * `network` and moves to the communication stream: the matched collective
+ * (examples/ae/scheduler/vllm/nanoflow.py:59-69), its fused substitute
+ * (vllm/nanoflow.py:171-211, flashinfer call) and the in-tree kernel
+ * fused_rs_ln_ag_cta (tokenweave-kernels/csrc/tokenweave.cu:38-198), without
+ * NVLS/multimem: plain peer loads and stores over NVLink.
+ *
+ * Each rank owns one "region" per micro-batch slot, mapped by all ranks:
+ *   region + df_comm_partial_offset : partial[max_rows, hidden] bf16 -- the rank's
+ *        down / o projection writes its partial sums here (pass it as the GEMM's C)
+ *   region + df_comm_sum_offset     : sum[max_rows, hidden] bf16 -- after the call,
+ *        the reduced rows (identical on every rank)
+ *   region + 0                      : flag words, zeroed at allocation
+ * Calls that use the same region must be ordered (same stream); every rank must
+ * issue the same sequence of calls on a region with the same T and n_ctas.
+ */
+#define DF_COMM_MAX_WORLD 8
+#define DF_COMM_MAX_CTAS 64
+
+typedef struct df_comm_rank {
+  int rank;                          /* this rank's index in [0, world)              */
+  void* regions[DF_COMM_MAX_WORLD];  /* region base of every rank, as mapped locally */
+  const void* residual_in;           /* [T, hidden] bf16 or NULL (= zeros); fused call only */
+  void* residual_out;                /* [T, hidden] bf16; may equal residual_in      */
+  void* out;                         /* [T, hidden] bf16 normalised output           */
+} df_comm_rank_t;
+
+/* Bytes of one region / byte offsets of its two buffers (0 on bad arguments). */
+size_t df_comm_region_bytes(int max_rows, int hidden);
+size_t df_comm_partial_offset(int max_rows, int hidden);
+size_t df_comm_sum_offset(int max_rows, int hidden);
+
+/* Set-up time only (these four are the library's only calls that allocate, map or
+ * free device memory, and they synchronise the device): allocate a zero-flagged
+ * region and export its 64-byte CUDA IPC handle; map a peer's region from its
+ * handle; unmap; free. The reference gets the same from
+ * torch.distributed._symmetric_memory (examples/ae/scheduler/vllm/tokenweave.py:97-110). */
+int df_comm_region_alloc(size_t bytes, void** dev_ptr, unsigned char ipc_handle[64]);
+int df_comm_region_open(const unsigned char ipc_handle[64], void** dev_ptr);
+int df_comm_region_close(void* peer_ptr);
+int df_comm_region_free(void* dev_ptr);
+
+/* sum = sum over ranks of partial, rows [0, T). n_ctas (<= DF_COMM_MAX_CTAS, <= 0
+ * means 32) is the number of 256-thread CTAs, i.e. how many SMs the reduction
+ * takes away from the GEMMs of the other micro-batch. */
+int df_allreduce_bf16(const df_comm_rank_t* view, int world, int max_rows, int hidden, int T, int n_ctas,
+                      df_status_t* dev_status, void* stream);
+
+/* The fused form: y = sum over ranks of partial; r' = y + residual_in;
+ * out = bf16(r' * rsqrt(mean(r'^2) + eps)) * weight; residual_out = r'.
+ * Rounding points as in tokenweave.cu:76-103 (bf16 residual, fp32 sum of squares). */
+int df_allreduce_add_rmsnorm_bf16(const df_comm_rank_t* view, int world, int max_rows, int hidden, int T,
+                                  const void* weight, float eps, int n_ctas, df_status_t* dev_status,
+                                  void* stream);
+
+/* Test vehicle: runs `world` ranks of the same kernel on ONE GPU as one cooperative
+ * launch (grid.y = rank), `views[r]` describing rank r, all regions in this GPU's
+ * memory. Exercises the flag protocol and the arithmetic without a second GPU.
+ * No counterpart in the reference. */
+int df_allreduce_emulated_bf16(const df_comm_rank_t* views, int world, int max_rows, int hidden, int T,
+                               const void* weight, float eps, int fuse_rmsnorm, int n_ctas,
+                               df_status_t* dev_status, void* stream);
 
 /* Size of the library-owned scratch behind df_mlp_gated_bf16_static: 64 MiB of
  * static device memory, held by every GPU that loads the library until the

@@ -1,0 +1,85 @@
+"""Worker of tests/test_gpu_multi.py: launched by torch.distributed.run, one rank per GPU."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main() -> None:
+    from dynaflow_b200 import ops
+    from dynaflow_b200.comm import PeerComm
+    from dynaflow_b200.layer import TensorParallelGatedMLP
+    from oracle import ops_oracle
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    T, H, I = 1000, 1024, 2048
+    comm = PeerComm(rank, world, max_rows=1024, hidden=H, slots=2, n_ctas=16, device=dev)
+
+    # ---- plain all-reduce: bit-exact against the fp32 rank-order sum, three calls in a row
+    parts = [torch.randn(T, H, generator=torch.Generator().manual_seed(100 + r)).bfloat16() for r in range(world)]
+    acc = torch.zeros(T, H)
+    for p in parts:
+        acc += p.float()
+    want = acc.bfloat16()
+    for call in range(3):
+        comm.partial(0, T).copy_(parts[rank])
+        got = comm.all_reduce(0, T)
+        torch.cuda.synchronize()
+        ops.check_status()
+        assert torch.equal(got.cpu(), want), f"rank {rank} call {call}: all-reduce differs"
+        dist.barrier()
+
+    # ---- fused residual + RMSNorm
+    g = torch.Generator().manual_seed(5)
+    residual = torch.randn(T, H, generator=g).bfloat16()
+    weight = (1 + 0.1 * torch.randn(H, generator=g)).bfloat16()
+    want_out, want_res = ops_oracle.allreduce_add_rmsnorm(parts, residual, weight)
+    comm.partial(1, T).copy_(parts[rank])
+    res_dev = residual.to(dev)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    comm.all_reduce_add_rmsnorm(1, T, res_dev, weight.to(dev), out, res_dev)   # residual updated in place
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(res_dev.cpu(), want_res), f"rank {rank}: residual differs"
+    rel = ((out.float().cpu() - want_out.float()).abs().max() / want_out.float().abs().max()).item()
+    assert rel <= 2e-2, f"rank {rank}: fused RMSNorm rel err {rel}"
+    dist.barrier()
+
+    # ---- tensor-parallel gated MLP, two micro-batches, reduction overlapped with the next GEMMs
+    g = torch.Generator().manual_seed(9)
+    w_gate = (torch.randn(I, H, generator=g) * 0.05).bfloat16()
+    w_up = (torch.randn(I, H, generator=g) * 0.05).bfloat16()
+    w_down = (torch.randn(H, I, generator=g) * 0.05).bfloat16()
+    x = torch.randn(2 * T, H, generator=g).bfloat16()
+    layer = TensorParallelGatedMLP(H, I, rank=rank, world=world, max_rows=1024, micro_batches=2, device=dev,
+                                   weights=(w_gate, w_up, w_down), comm=comm)
+    results = []
+    layer.forward_device(x.to(dev), None, [0, T, 2 * T], results=results)
+    torch.cuda.synchronize()
+    ops.check_status()
+    got = torch.cat([r.cpu() for r in results])
+    want = ops_oracle.gated_mlp(x, w_gate, w_up, w_down)
+    rel = ((got.float() - want.float()).abs().max() / want.float().abs().max()).item()
+    assert rel <= 2e-2, f"rank {rank}: TP layer rel err {rel}"
+    out_host = torch.empty(2 * T, H, dtype=torch.bfloat16).pin_memory()
+    layer.forward_host(x.pin_memory(), out_host, [0, T, 2 * T])
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(out_host, got), f"rank {rank}: host-staged step differs from the device-resident one"
+    dist.barrier()
+    comm.close()
+    dist.destroy_process_group()
+    if rank == 0:
+        print("MULTI_GPU_OK")
+
+
+if __name__ == "__main__":
+    main()
