@@ -4,24 +4,35 @@
 //   mode PLAIN  : C[M,N]  = A[M,K] * B[N,K]^T
 //   mode GATEUP : Hd[M,I] = silu(X * Wg^T) (.) (X * Wu^T)
 //
-// One CTA per SM, 256 threads:
-//   warp 0      TMA producer (one lane): fills a 4-stage ring of
-//               {A 128x64, B 256x64} bf16 tiles, 128-byte swizzled
-//   warp 1      MMA issuer (one lane): 4 x tcgen05.mma 128x256x16 per stage
-//               into one of two 256-column fp32 accumulators
+// Two variants of one kernel template:
+//
+//   CTAS == 2 (opt-in, DF_GEMM_CTAS=2): a cluster of two CTAs on neighbouring SMs
+//     computes one 256 x 256 accumulator tile with tcgen05.mma.cta_group::2.
+//     Each CTA stages its own 128 rows of A and ONE HALF of the B tile
+//     (128 of the 256 B rows), so a CTA moves 32 KB per 64-wide k-block through
+//     L2 -> shared memory instead of 48 KB, and six stages fit instead of four.
+//     Every CTA issues its own (plain, non-broadcast) TMA loads; their bytes are
+//     counted on the leader CTA's mbarrier. The leader's single MMA thread drives
+//     both SMs' tensor cores; each CTA's epilogue drains its own 128 TMEM lanes.
+//   CTAS == 1 (default): one CTA per 128 x 256 tile, four 48 KB stages.
+//
+// 256 threads per CTA:
+//   warp 0      TMA producer (one lane)
+//   warp 1      MMA issuer (one lane; leader CTA only when CTAS == 2)
 //   warp 2      allocates / frees the 512 tensor-memory columns
 //   warps 4..7  epilogue: tcgen05.ld of the finished accumulator, SiLU*mul or
 //               plain conversion, 16-byte global stores; runs under the MMAs
 //               of the next tile thanks to the second accumulator
 //
-// In GATEUP mode the B stage is two 128-row boxes, rows [i0,i0+128) of W_gate
-// and of W_up, so the accumulator holds gate in columns [0,128) and up in
+// In GATEUP mode the two B halves of a stage are rows [i0,i0+128) of W_gate and
+// of W_up, so the accumulator holds gate in columns [0,128) and up in
 // [128,256) for the same 128 output columns.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -31,18 +42,23 @@
 
 namespace df {
 
-constexpr int BM = 128;
+constexpr int BM = 128;        // rows of A (and of the accumulator) per CTA
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int ACC_COLS = 256;  // fp32 accumulator columns per tile (= MMA N)
-constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;
 constexpr int B_HALF_BYTES = 128 * BK * 2;
-constexpr int B_BYTES = 2 * B_HALF_BYTES;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int GEMM_THREADS = 256;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+template <int CTAS>
+struct TileCfg {
+  static constexpr int kStages = (CTAS == 2) ? 6 : 4;
+  static constexpr int kBBytes = (CTAS == 2) ? B_HALF_BYTES : 2 * B_HALF_BYTES;  // per CTA
+  static constexpr int kStageBytes = A_BYTES + kBBytes;
+  static constexpr int kTileM = BM * CTAS;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
 
 enum : int { MODE_PLAIN = 0, MODE_GATEUP = 1 };
 enum : unsigned { WHERE_PRODUCER = 1, WHERE_MMA_FULL = 2, WHERE_MMA_TMEM = 3, WHERE_EPILOGUE = 4 };
@@ -51,6 +67,7 @@ struct GemmParams {
   int M, N, K;  // N = output columns (I in GATEUP mode)
   int ldc;
   int tiles_m, tiles_n, num_tiles, num_kb, group_m;
+  int debug;  // development only: bit 0 = producer skips the copies, bit 1 = epilogue skips the stores
   unsigned long long timeout_ns;
   __nv_bfloat16* C;
   Status* status;
@@ -58,7 +75,7 @@ struct GemmParams {
 
 // Tile order: groups of `group_m` row panels; inside a group the row panel
 // varies fastest, so the CTAs of one wave share few distinct A and B tiles
-// and those stay in L2.
+// and those stay in L2, and the weights stream from HBM once per group.
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int t, int& m_blk, int& n_blk) {
   const int per_group = p.group_m * p.tiles_n;
   const int group = t / per_group;
@@ -76,10 +93,13 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 
 __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
-template <int MODE>
+template <int MODE, int CTAS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
                const __grid_constant__ CUtensorMap tm_b1, const GemmParams p) {
+  using Cfg = TileCfg<CTAS>;
+  constexpr int STAGES = Cfg::kStages;
+  constexpr int STAGE_BYTES = Cfg::kStageBytes;
   constexpr int BN_OUT = (MODE == MODE_GATEUP) ? 128 : 256;
 
   extern __shared__ uint8_t smem_raw[];
@@ -95,6 +115,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = (CTAS == 2) ? cluster_ctarank() : 0u;  // 0 = leader
+  const int unit = (CTAS == 2) ? (blockIdx.x >> 1) : blockIdx.x;   // CTA or CTA pair
+  const int num_units = (CTAS == 2) ? (gridDim.x >> 1) : gridDim.x;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -103,7 +126,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
-      mbar_init(&tempty[a], 128);
+      mbar_init(&tempty[a], (CTAS == 2) ? 8 : 128);  // CTAS == 2: one arrival per epilogue warp of both CTAs
     }
     *abort_flag = 0u;
     mbar_fence_init();
@@ -112,11 +135,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     tma_prefetch_desc(&tm_b1);
   }
   if (warp == 2) {
-    tmem_alloc(tmem_slot, TMEM_COLS);
-    tmem_relinquish();
+    if (CTAS == 2) {
+      tmem_alloc_2cta(tmem_slot, TMEM_COLS);
+      tmem_relinquish_2cta();
+    } else {
+      tmem_alloc(tmem_slot, TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if (CTAS == 2) {
+    cluster_sync();  // the peer's barriers exist before anything signals them
+  } else {
+    __syncthreads();
+  }
   tc_fence_after();
 
   const uint32_t tmem_base = *tmem_slot;
@@ -128,13 +160,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x) {
+      for (int t = unit; ok && t < p.num_tiles; t += num_units) {
         int m_blk, n_blk;
         tile_coords(p, t, m_blk, n_blk);
-        const int m0 = m_blk * BM;
+        const int m0 = m_blk * Cfg::kTileM + static_cast<int>(cta_rank) * BM;
         const int n0 = n_blk * BN_OUT;
-        const int y1 = (MODE == MODE_GATEUP) ? n0 : n0 + 128;
-        const CUtensorMap* map1 = (MODE == MODE_GATEUP) ? &tm_b1 : &tm_b0;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, dl, WHERE_PRODUCER, t)) {
             ok = false;
@@ -142,10 +172,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           }
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
-          mbar_expect_tx(&full[stage], STAGE_BYTES);
-          tma_load_2d(sa, &tm_a, &full[stage], kb * BK, m0);
-          tma_load_2d(sb, &tm_b0, &full[stage], kb * BK, n0);
-          tma_load_2d(sb + B_HALF_BYTES, map1, &full[stage], kb * BK, y1);
+          if (p.debug & 1) {
+            if (cta_rank == 0) mbar_arrive(&full[stage]);
+          } else if (CTAS == 2) {
+            // this CTA's half of B: gate rows on the leader, up rows on its peer (GATEUP);
+            // B rows [n0, n0+128) on the leader and [n0+128, n0+256) on its peer (PLAIN)
+            const CUtensorMap* map_b = (MODE == MODE_GATEUP && cta_rank == 1) ? &tm_b1 : &tm_b0;
+            const int yb = (MODE == MODE_GATEUP) ? n0 : n0 + static_cast<int>(cta_rank) * 128;
+            // both CTAs' bytes are counted on the leader's barrier, which the MMA thread waits on
+            const uint32_t bar = mapa_shared(smem_u32(&full[stage]), 0u);
+            if (cta_rank == 0) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);
+            tma_load_2d_2cta(sa, &tm_a, bar, kb * BK, m0);
+            tma_load_2d_2cta(sb, map_b, bar, kb * BK, yb);
+          } else {
+            const int y1 = (MODE == MODE_GATEUP) ? n0 : n0 + 128;
+            const CUtensorMap* map1 = (MODE == MODE_GATEUP) ? &tm_b1 : &tm_b0;
+            mbar_expect_tx(&full[stage], STAGE_BYTES);
+            tma_load_2d(sa, &tm_a, &full[stage], kb * BK, m0);
+            tma_load_2d(sb, &tm_b0, &full[stage], kb * BK, n0);
+            tma_load_2d(sb + B_HALF_BYTES, map1, &full[stage], kb * BK, y1);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -156,13 +202,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     __syncwarp();
   } else if (warp == 1) {
     // -------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, ACC_COLS);
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM * CTAS, ACC_COLS);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < p.num_tiles; t += gridDim.x, ++it) {
+      for (int t = unit; ok && t < p.num_tiles; t += num_units, ++it) {
         const int acc = it & 1;
         const uint32_t aphase = (it >> 1) & 1u;
         if (!mbar_wait(&tempty[acc], aphase ^ 1u, dl, WHERE_MMA_TMEM, t)) break;
@@ -180,15 +226,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advancing 16 elements along K = 32 bytes = 2 descriptor units
-            umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (CTAS == 2) {
+              umma_bf16_2cta(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            } else {
+              umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
           }
-          umma_commit(&empty[stage]);
+          if (CTAS == 2) {
+            if (p.debug & 4) {
+              umma_commit_2cta_mask(&empty[stage], 3);
+            } else {
+              umma_commit_2cta(&empty[stage]);  // frees the stage in both CTAs
+            }
+          } else {
+            umma_commit(&empty[stage]);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) umma_commit(&tfull[acc]);
+        if (ok) {
+          if (CTAS == 2) {
+            if (p.debug & 4) {
+              umma_commit_2cta_mask(&tfull[acc], 3);
+            } else {
+              umma_commit_2cta(&tfull[acc]);
+            }
+          } else {
+            umma_commit(&tfull[acc]);
+          }
+        }
       }
     }
     __syncwarp();
@@ -196,11 +264,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     // ---------------------------------------------------------- epilogue
     const int q = warp - 4;  // == warp % 4: the TMEM lane quarter this warp may read
     int it = 0;
-    for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++it) {
+    for (int t = unit; t < p.num_tiles; t += num_units, ++it) {
       int m_blk, n_blk;
       tile_coords(p, t, m_blk, n_blk);
       const int n0 = n_blk * BN_OUT;
-      const int row = m_blk * BM + q * 32 + lane;
+      const int row = m_blk * Cfg::kTileM + static_cast<int>(cta_rank) * BM + q * 32 + lane;
       const int acc = it & 1;
       const uint32_t aphase = (it >> 1) & 1u;
       bool ok = mbar_wait(&tfull[acc], aphase, dl, WHERE_EPILOGUE, t);
@@ -209,7 +277,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       tc_fence_after();
       const uint32_t t_acc = tmem_base + static_cast<uint32_t>(acc * ACC_COLS) + (static_cast<uint32_t>(q * 32) << 16);
       __nv_bfloat16* crow = p.C + static_cast<size_t>(row) * p.ldc;
-      const bool row_ok = row < p.M;
+      const bool row_ok = row < p.M && !(p.debug & 2);
 
       if (MODE == MODE_GATEUP) {
 #pragma unroll 1
@@ -262,14 +330,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         }
       }
       tc_fence_before();
-      mbar_arrive(&tempty[acc]);
+      if (CTAS == 2) {
+        // the accumulator is free again once every epilogue warp of BOTH CTAs has drained it;
+        // the MMA thread that waits for that lives in the leader CTA
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0u));
+      } else {
+        mbar_arrive(&tempty[acc]);
+      }
     }
   }
 
   // ------------------------------------------------------------ teardown
   __syncwarp();
   tc_fence_before();
-  __syncthreads();
+  if (CTAS == 2) {
+    cluster_sync();  // nothing of the pair touches the other CTA's shared or tensor memory after this
+  } else {
+    __syncthreads();
+  }
   if (warp == 2) {
     tc_fence_after();
     if (*abort_flag) {
@@ -278,7 +357,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       const uint64_t t_stop = globaltimer_ns() + 2000000ull;
       while (globaltimer_ns() < t_stop) __nanosleep(1000);
     }
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (CTAS == 2) {
+      tmem_dealloc_2cta(tmem_base, TMEM_COLS);
+    } else {
+      tmem_dealloc(tmem_base, TMEM_COLS);
+    }
   }
 }
 
@@ -304,7 +387,90 @@ static bool make_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uin
   return true;
 }
 
+// Development knob: integer taken from the environment on every launch (cheap: getenv).
+static int tuning_int(const char* name, int fallback) {
+  const char* v = std::getenv(name);
+  if (v == nullptr || *v == '\0') return fallback;
+  const int x = std::atoi(v);
+  return x >= 0 ? x : fallback;
+}
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// How many CTA pairs of the 2-CTA kernel can be resident at once on the current
+// device (cached per device and mode); 0 if the query fails.
+template <int MODE>
+static int max_active_pairs() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (cached[dev] != 0) return cached[dev] > 0 ? cached[dev] : 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * 256, 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = TileCfg<2>::kSmemBytes;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  cudaError_t e = cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<MODE, 2>, &cfg);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    n = 0;
+  }
+  cached[dev] = n > 0 ? n : -1;
+  return n;
+}
+
+template <int MODE, int CTAS>
+static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b0, const CUtensorMap& tm_b1, GemmParams p,
+                          int max_ctas, int sms, cudaStream_t stream) {
+  using Cfg = TileCfg<CTAS>;
+  constexpr int BN_OUT = (MODE == MODE_GATEUP) ? 128 : 256;
+  // the attribute is per device; setting it on every call is cheap and covers every device that launches
+  const cudaError_t attr_err =
+      cudaFuncSetAttribute(gemm_tc_kernel<MODE, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  if (attr_err != cudaSuccess) return fail(DF_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(attr_err));
+
+  p.tiles_m = (p.M + Cfg::kTileM - 1) / Cfg::kTileM;
+  p.tiles_n = (p.N + BN_OUT - 1) / BN_OUT;
+  p.num_tiles = p.tiles_m * p.tiles_n;
+  p.group_m = tuning_int("DF_GEMM_GROUP_M", 32) / CTAS;  // row panels of kTileM rows: the same rows per group
+  if (p.group_m < 1) p.group_m = 1;
+
+  int units = (CTAS == 2) ? max_active_pairs<MODE>() : sms;
+  if (units <= 0) units = sms / CTAS;
+  if (max_ctas > 0 && max_ctas / CTAS < units) units = max_ctas / CTAS;
+  if (units < 1) units = 1;
+  if (p.num_tiles < units) units = p.num_tiles;
+
+  if (tuning_int("DF_DEBUG", 0) > 0)
+    std::fprintf(stderr, "[df] gemm mode=%d ctas=%d M=%d N=%d K=%d tiles=%d grid=%d group_m=%d\n", MODE, CTAS, p.M, p.N,
+                 p.K, p.num_tiles, units * CTAS, p.group_m);
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(units * CTAS, 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = CTAS;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<MODE, CTAS>, tm_a, tm_b0, tm_b1, p);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(DF_ECUDA, "gemm launch (%d-CTA tiles): %s", CTAS, cudaGetErrorString(e));
+  }
+  return DF_OK;
+}
 
 template <int MODE>
 static int launch_gemm(const void* a, const void* b0, const void* b1, void* c, int M, int N, int K, int lda, int ldb,
@@ -321,42 +487,31 @@ static int launch_gemm(const void* a, const void* b0, const void* b1, void* c, i
   int sms = df_sm_count();
   if (sms <= 0) return fail(DF_ECUDA, "no CUDA device");
 
-  static std::once_flag once[2];
-  static cudaError_t attr_err[2] = {cudaSuccess, cudaSuccess};
-  // the attribute is per device; set it on every call (cheap) so that every device that launches has it
-  attr_err[MODE] = cudaFuncSetAttribute(gemm_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-  (void)once;
-  if (attr_err[MODE] != cudaSuccess)
-    return fail(DF_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(attr_err[MODE]));
-
   CUtensorMap tm_a, tm_b0, tm_b1;
   if (!make_map_bf16(&tm_a, a, M, K, lda, BM)) return DF_ECUDA;
   if (!make_map_bf16(&tm_b0, b0, N, K, ldb, 128)) return DF_ECUDA;
   if (!make_map_bf16(&tm_b1, b1, N, K, ldb, 128)) return DF_ECUDA;
 
-  constexpr int BN_OUT = (MODE == MODE_GATEUP) ? 128 : 256;
   GemmParams p;
   p.M = M;
   p.N = N;
   p.K = K;
   p.ldc = ldc;
-  p.tiles_m = (M + BM - 1) / BM;
-  p.tiles_n = (N + BN_OUT - 1) / BN_OUT;
-  p.num_tiles = p.tiles_m * p.tiles_n;
   p.num_kb = (K + BK - 1) / BK;
-  p.group_m = 8;
   p.timeout_ns = timeout_ns();
   p.C = static_cast<__nv_bfloat16*>(c);
   p.status = reinterpret_cast<Status*>(dev_status);
+  p.tiles_m = p.tiles_n = p.num_tiles = p.group_m = 0;
+  p.debug = tuning_int("DF_GEMM_DEBUG", 0);
 
-  int grid = sms;
-  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  if (p.num_tiles < grid) grid = p.num_tiles;
-
-  gemm_tc_kernel<MODE><<<grid, GEMM_THREADS, SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(tm_a, tm_b0, tm_b1, p);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return fail(DF_ECUDA, "gemm launch: %s", cudaGetErrorString(e));
-  return DF_OK;
+  // One CTA per tile is the default: measured on B200 under the power cap, the CTA-pair
+  // variant moves a third less data from L2 but keeps the tensor pipe slightly less busy
+  // (67 % vs 75 % active on a 1024-row gate/up launch), and the two end up within +-3 %.
+  // DF_GEMM_CTAS=2 selects the pair variant.
+  const int want = tuning_int("DF_GEMM_CTAS", 1);
+  const bool two = want == 2 && M > BM && (max_ctas <= 0 || max_ctas >= 2);
+  if (two) return launch_variant<MODE, 2>(tm_a, tm_b0, tm_b1, p, max_ctas, sms, static_cast<cudaStream_t>(stream));
+  return launch_variant<MODE, 1>(tm_a, tm_b0, tm_b1, p, max_ctas, sms, static_cast<cudaStream_t>(stream));
 }
 
 }  // namespace df
