@@ -18,12 +18,18 @@ class CUDAGraphConfig:
     ``check_ptr_consistency`` makes a replay verify that the input tensors still
     live at the captured addresses. ``weak_ref_output`` is accepted for
     compatibility; captured outputs are always owned by the capture entry here.
+
+    ``copy_mismatched_inputs`` (not in the reference) turns the pointer check into a
+    repair: an input that arrives at another address than the captured one -- the
+    output of an eagerly executed or substituted subgraph -- is copied into the
+    captured input before the replay instead of raising.
     """
 
     enabled: bool
     capture_sizes: list[int]
     weak_ref_output: bool = True
     check_ptr_consistency: bool = True
+    copy_mismatched_inputs: bool = False
 
 
 @dataclasses.dataclass

@@ -6,7 +6,8 @@ pair is seen must be a dry run, which captures into the memory pool of that
 nano-batch index; later calls check that inputs still live at the captured
 addresses (``RuntimeError`` otherwise), replay, and return the captured outputs.
 
-Differences: captured outputs are held by the entry itself instead of through
+Differences: with ``CUDAGraphConfig.copy_mismatched_inputs`` a moved input is copied
+into its captured location instead of raising; captured outputs are held by the entry itself instead of through
 vLLM's ``weak_ref_tensor`` custom op (``cudagraph.py:37-65``), so no third-party
 extension is needed; pools are keyed per nano-batch index exactly as in
 ``cudagraph.py:11-31`` and an optional hook lets a host share them with its
@@ -69,10 +70,16 @@ class CUDAGraphWrapper:
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, pool=_global_pool.get_pool(handle.batch_idx)):
                 out = self.runnable(*args, **kwargs)
-            self._entries[key] = {"graph": graph, "out": out, "inputs": _tensor_addresses(args)}
+            self._entries[key] = {"graph": graph, "out": out, "inputs": _tensor_addresses(args),
+                                  "static_inputs": [a for a in args if isinstance(a, torch.Tensor)]}
             return out
 
-        if self.config.check_ptr_consistency and _tensor_addresses(args) != entry["inputs"]:
+        if getattr(self.config, "copy_mismatched_inputs", False):
+            live = [a for a in args if isinstance(a, torch.Tensor)]
+            for captured, new in zip(entry["static_inputs"], live):
+                if captured.data_ptr() != new.data_ptr():
+                    captured.copy_(new)  # on the current stream, ahead of the replay
+        elif self.config.check_ptr_consistency and _tensor_addresses(args) != entry["inputs"]:
             raise RuntimeError("CUDAGraph input addresses changed between capture and replay")
         entry["graph"].replay()
         return entry["out"]

@@ -27,6 +27,28 @@ from .matching import MatchingRule
 from .utils import pack_tokens
 
 
+def gated_mlp_rule() -> MatchingRule:
+    """Matches a Hugging Face style gated MLP as ONE subgraph: gate linear, SiLU, up
+    linear, product, down linear, in the order Dynamo traces
+    ``down_proj(act_fn(gate_proj(x)) * up_proj(x))``."""
+    from .matching import Op
+
+    return MatchingRule(condition=(Op("linear"), Op("silu"), Op("linear"), Op("mul"), Op("linear")))
+
+
+def native_gated_mlp(x: torch.Tensor, rows: Any, w_gate: torch.Tensor, w_up: torch.Tensor,
+                     w_down: torch.Tensor) -> torch.Tensor:
+    """Substitute for the subgraph cut by ``gated_mlp_rule``: its arguments arrive in
+    graph order (activation, row count, gate / up / down weights in ``nn.Linear``
+    layout). Runs the fused sm_100a kernels on the current stream."""
+    from . import ops
+
+    flat = x.reshape(-1, x.shape[-1])
+    if not flat.is_contiguous():
+        flat = flat.contiguous()
+    return ops.gated_mlp(flat, w_gate, w_up, w_down).view(*x.shape[:-1], w_down.shape[0])
+
+
 def _make_stream() -> Any:
     return torch.cuda.Stream() if torch.cuda.is_available() else None
 

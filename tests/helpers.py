@@ -12,10 +12,11 @@ from dynaflow_b200.matching import MatchingRule, Op
 from dynaflow_b200.policies import NanoFlowScheduler
 
 
-def make_config(max_splits=2, capture_sizes=(64, 128, 256), cudagraph=False, **additional):
+def make_config(max_splits=2, capture_sizes=(64, 128, 256), cudagraph=False, copy_inputs=False, **additional):
     additional.setdefault("min_nano_split_tokens", 1)
     return DynaFlowConfig("unused:unused", max_splits, InductorConfig(False),
-                          CUDAGraphConfig(cudagraph, list(capture_sizes)), dict(additional))
+                          CUDAGraphConfig(cudagraph, list(capture_sizes), copy_mismatched_inputs=copy_inputs),
+                          dict(additional))
 
 
 def cut_policy(pattern, tag, config=None, cls=NanoFlowScheduler):
