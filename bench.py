@@ -237,6 +237,34 @@ def run_ours(args) -> None:
     down_ms = statistics.mean(m1.elapsed_time(m2) for step in marks for (_m0, m1, m2) in step)
     ops.check_status()
 
+    # ---- N > 1: how much of the reduction hides under the other micro-batch's GEMMs
+    comm_stats = None
+    if world > 1:
+        def timed(**kw):
+            for _ in range(3):
+                layer.forward_device(x_dev, out_dev, cuts, **kw)
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            reps = max(10, args.steps // 4)
+            for _ in range(reps):
+                layer.forward_device(x_dev, out_dev, cuts, **kw)
+            b.record()
+            barrier()
+            return max_over_ranks(a.elapsed_time(b) / reps)
+
+        t_compute = timed(skip_comm=True)
+        t_comm = timed(skip_compute=True)
+        payload = ROWS * H * 2  # bytes reduced per step (all micro-batches)
+        wire = 2.0 * (world - 1) / world * payload
+        comm_stats = {"ms_overlapped": ms_step, "ms_compute_only": t_compute, "ms_comm_only": t_comm,
+                      "hidden_frac": 1.0 - (ms_step - t_compute) / t_comm,
+                      "bus_gbs_comm_only": wire / (t_comm * 1e-3) / 1e9,
+                      "nvlink_peak_gbs": 770.0, "nvlink_peak_source": "measured peer copy, per direction",
+                      "roofline_ms": max(6.0 * ROWS * H * (I // world) / (float(measured_peaks()[0]["bf16_tflops"]) * 1e12),
+                                         (world - 1) / world * payload / 770e9) * 1e3}
+        ops.check_status()
+
     # ---- end to end: pinned host buffers, copies inside the timed region
     for _ in range(args.warmup):
         layer.forward_host(x_host, out_host, cuts)
@@ -279,6 +307,10 @@ def run_ours(args) -> None:
         cpu = {"value": rate, "unit": "tokens/s", "cores": _t.get_num_threads(), "kind": "port",
                "sample": f"{rows} of {ROWS} rows, one pass of the oracle's gated MLP in {secs:.1f} s (bf16, torch CPU)"}
 
+    sweep = None
+    if world == 1 and not args.no_sweep:
+        sweep = m_sweep(layer, dev, peaks)
+
     line = {
         "metric": METRIC, "value": ROWS / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
@@ -296,11 +328,69 @@ def run_ours(args) -> None:
         "mlp_pct_tensor_peak": 100.0 * step_flops / (ms_step * 1e-3) / 1e12 / peak,
         "clocks": sampler.summary(t_wall0, t_wall1) if sampler is not None else None,
         "cpu_baseline": cpu,
+        "sweep": sweep,
     }
     if world > 1:
-        line["comm"] = layer.comm_summary()
+        line["comm"] = dict(layer.comm_summary(), **(comm_stats or {}))
         dist.destroy_process_group()
     print(json.dumps(line))
+
+
+def m_sweep(layer, dev, peaks) -> list[dict]:
+    """The M sweep of the fused-MLP configuration: two micro-batches of M/2 rows, serial (one
+    stream) and overlapped (one stream per micro-batch), against max(flops / tensor peak,
+    bytes / HBM peak)."""
+    import torch
+
+    from dynaflow_b200 import ops
+
+    out = []
+    streams = layer.streams
+    for rows in (16, 256, 2048, 8192, 16384):
+        half = rows // 2
+        x = torch.randn(rows, H, device=dev).bfloat16()
+        y = torch.empty(rows, H, dtype=torch.bfloat16, device=dev)
+        hs = [layer.h_views[i][:half] for i in range(2)]
+
+        def serial():
+            for i in range(2):
+                ops.gated_mlp(x[i * half:(i + 1) * half], layer.w_gate, layer.w_up, layer.w_down,
+                              out=y[i * half:(i + 1) * half], workspace=layer.workspaces[i])
+
+        def overlapped():
+            main = torch.cuda.current_stream()
+            fork = torch.cuda.Event()
+            fork.record(main)
+            for i in range(2):
+                streams[i].wait_event(fork)
+                with torch.cuda.stream(streams[i]):
+                    ops.gated_mlp(x[i * half:(i + 1) * half], layer.w_gate, layer.w_up, layer.w_down,
+                                  out=y[i * half:(i + 1) * half], workspace=layer.workspaces[i])
+                main.wait_stream(streams[i])
+
+        def time_it(fn):
+            for _ in range(5):
+                fn()
+            torch.cuda.synchronize()
+            n = 200 if rows <= 2048 else 40
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(n):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / n
+
+        t_serial, t_overlap = time_it(serial), time_it(overlapped)
+        flops = 6.0 * rows * H * I
+        bytes_min = 3.0 * H * I * 2 + 2.0 * rows * H * 2
+        bound_ms = max(flops / (float(peaks["bf16_tflops"]) * 1e12), bytes_min / (float(peaks["hbm_gbs"]) * 1e9)) * 1e3
+        out.append({"rows": rows, "ms_serial": t_serial, "ms_overlapped": t_overlap, "tflops_serial": flops / t_serial / 1e9,
+                    "roofline_ms": bound_ms, "frac_of_roofline": bound_ms / min(t_serial, t_overlap),
+                    "bound": "tensor" if flops / (float(peaks["bf16_tflops"]) * 1e12) > bytes_min / (float(peaks["hbm_gbs"]) * 1e9) else "hbm"})
+        del hs
+    ops.check_status()
+    return out
 
 
 def main() -> None:
@@ -313,6 +403,7 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=ROWS, help="rows per step (default: the benchmark's 16384; "
                     "smaller values are for profiler captures only)")
     ap.add_argument("--comm-ctas", type=int, default=32, help="CTAs of the peer-memory all-reduce kernel (N > 1)")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the M sweep (profiling runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     args = ap.parse_args()
     if args.rows != ROWS:

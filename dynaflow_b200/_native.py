@@ -45,6 +45,9 @@ SIGNATURES: dict[str, tuple] = {
     "df_status_clear": (_i, [_vp, _vp]),
     "df_gemm_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "df_gateup_silu_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
+    "df_gemm_splitk_workspace_bytes": (_sz, []),
+    "df_gemm_bf16_ws": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp, _vp]),
+    "df_gateup_silu_bf16_ws": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp, _vp]),
     "df_mlp_workspace_bytes": (_sz, [_i, _i, _i]),
     "df_mlp_gated_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "df_comm_region_bytes": (_sz, [_i, _i]),

@@ -67,6 +67,12 @@ struct GemmParams {
   int M, N, K;  // N = output columns (I in GATEUP mode)
   int ldc;
   int tiles_m, tiles_n, num_tiles, num_kb, group_m;
+  // Stream-K (1-CTA tiles only; sk_per == 0 means off): the launch's k-blocks, tile after
+  // tile, are cut into equal ranges of sk_per units, one range per CTA, so that every SM
+  // streams its share of the weights even when there are fewer tiles than SMs.
+  int sk_per;
+  float* sk_partials;        // [grid][256 columns][128 rows] fp32, column-major per CTA
+  unsigned int* sk_counters;  // [num_tiles] partial segments delivered, zero at launch
   int debug;  // development only: bit 0 = producer skips the copies, bit 1 = epilogue skips the stores
   unsigned long long timeout_ns;
   __nv_bfloat16* C;
@@ -92,6 +98,54 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 
 __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// One stretch of consecutive k-blocks of one tile, processed by one CTA (or CTA pair).
+struct Segment {
+  int tile, kb0, kb1;
+};
+
+// The sequence of segments of a CTA. Data-parallel: whole tiles unit, unit + num_units, ...
+// Stream-K: the units [unit * sk_per, (unit + 1) * sk_per) of the tile-major k-block sequence,
+// cut at tile boundaries. All three warp roles walk the same sequence.
+struct SegmentIter {
+  int cur, end, step, num_kb;
+  bool streamk;
+  __device__ SegmentIter(const GemmParams& p, int unit, int num_units) {
+    num_kb = p.num_kb;
+    streamk = p.sk_per > 0;
+    if (streamk) {
+      const long long total = static_cast<long long>(p.num_tiles) * p.num_kb;
+      const long long b = static_cast<long long>(unit) * p.sk_per;
+      const long long e = b + p.sk_per;
+      cur = static_cast<int>(b < total ? b : total);
+      end = static_cast<int>(e < total ? e : total);
+      step = 0;
+    } else {
+      cur = unit;
+      end = p.num_tiles;
+      step = num_units;
+    }
+  }
+  __device__ bool next(Segment& s) {
+    if (cur >= end) return false;
+    if (streamk) {
+      s.tile = cur / num_kb;
+      s.kb0 = cur - s.tile * num_kb;
+      const int tile_end = (s.tile + 1) * num_kb;
+      const int stop = tile_end < end ? tile_end : end;
+      s.kb1 = s.kb0 + (stop - cur);
+      cur = stop;
+    } else {
+      s.tile = cur;
+      s.kb0 = 0;
+      s.kb1 = num_kb;
+      cur += step;
+    }
+    return true;
+  }
+};
+
+enum : unsigned { WHERE_SK_PARTIALS = 5 };
 
 template <int MODE, int CTAS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -156,20 +210,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int t = unit; ok && t < p.num_tiles; t += num_units) {
-        int m_blk, n_blk;
-        tile_coords(p, t, m_blk, n_blk);
-        const int m0 = m_blk * Cfg::kTileM + static_cast<int>(cta_rank) * BM;
-        const int n0 = n_blk * BN_OUT;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(&empty[stage], phase ^ 1u, dl, WHERE_PRODUCER, t)) {
-            ok = false;
-            break;
-          }
+    // Lane 0 issues the tile copies. (Prefetching operand boxes or weight-row chunks into L2
+    // ahead of the copies was measured and made every shape slower, by 20 % to 3x.)
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    SegmentIter segs(p, unit, num_units);
+    Segment sg;
+    while (ok && segs.next(sg)) {
+      const int t = sg.tile;
+      int m_blk, n_blk;
+      tile_coords(p, t, m_blk, n_blk);
+      const int m0 = m_blk * Cfg::kTileM + static_cast<int>(cta_rank) * BM;
+      const int n0 = n_blk * BN_OUT;
+      const int y1_1cta = (MODE == MODE_GATEUP) ? n0 : n0 + 128;
+
+      for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+        if (lane == 0) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, dl, WHERE_PRODUCER, t)) ok = false;
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
+        if (lane == 0) {
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           if (p.debug & 1) {
@@ -185,17 +247,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             tma_load_2d_2cta(sa, &tm_a, bar, kb * BK, m0);
             tma_load_2d_2cta(sb, map_b, bar, kb * BK, yb);
           } else {
-            const int y1 = (MODE == MODE_GATEUP) ? n0 : n0 + 128;
             const CUtensorMap* map1 = (MODE == MODE_GATEUP) ? &tm_b1 : &tm_b0;
             mbar_expect_tx(&full[stage], STAGE_BYTES);
             tma_load_2d(sa, &tm_a, &full[stage], kb * BK, m0);
             tma_load_2d(sb, &tm_b0, &full[stage], kb * BK, n0);
-            tma_load_2d(sb + B_HALF_BYTES, map1, &full[stage], kb * BK, y1);
+            tma_load_2d(sb + B_HALF_BYTES, map1, &full[stage], kb * BK, y1_1cta);
           }
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
-          }
+        }
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
         }
       }
     }
@@ -208,13 +269,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = unit; ok && t < p.num_tiles; t += num_units, ++it) {
+      SegmentIter segs(p, unit, num_units);
+      Segment sg;
+      for (; ok && segs.next(sg); ++it) {
+        const int t = sg.tile;
         const int acc = it & 1;
         const uint32_t aphase = (it >> 1) & 1u;
         if (!mbar_wait(&tempty[acc], aphase ^ 1u, dl, WHERE_MMA_TMEM, t)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * ACC_COLS);
-        for (int kb = 0; kb < p.num_kb; ++kb) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(&full[stage], phase, dl, WHERE_MMA_FULL, t)) {
             ok = false;
             break;
@@ -227,9 +291,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advancing 16 elements along K = 32 bytes = 2 descriptor units
             if (CTAS == 2) {
-              umma_bf16_2cta(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              umma_bf16_2cta(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb > sg.kb0 || k > 0) ? 1u : 0u);
             } else {
-              umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+              umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb > sg.kb0 || k > 0) ? 1u : 0u);
             }
           }
           if (CTAS == 2) {
@@ -264,11 +328,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     // ---------------------------------------------------------- epilogue
     const int q = warp - 4;  // == warp % 4: the TMEM lane quarter this warp may read
     int it = 0;
-    for (int t = unit; t < p.num_tiles; t += num_units, ++it) {
+    SegmentIter segs(p, unit, num_units);
+    Segment sg;
+    for (; segs.next(sg); ++it) {
+      const int t = sg.tile;
       int m_blk, n_blk;
       tile_coords(p, t, m_blk, n_blk);
       const int n0 = n_blk * BN_OUT;
-      const int row = m_blk * Cfg::kTileM + static_cast<int>(cta_rank) * BM + q * 32 + lane;
+      const int row_in_tile = q * 32 + lane;
+      const int row = m_blk * Cfg::kTileM + static_cast<int>(cta_rank) * BM + row_in_tile;
       const int acc = it & 1;
       const uint32_t aphase = (it >> 1) & 1u;
       bool ok = mbar_wait(&tfull[acc], aphase, dl, WHERE_EPILOGUE, t);
@@ -278,6 +346,71 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       const uint32_t t_acc = tmem_base + static_cast<uint32_t>(acc * ACC_COLS) + (static_cast<uint32_t>(q * 32) << 16);
       __nv_bfloat16* crow = p.C + static_cast<size_t>(row) * p.ldc;
       const bool row_ok = row < p.M && !(p.debug & 2);
+
+      // ---- stream-K: a segment that does not start at k = 0 only delivers its fp32 partial
+      // sums; the CTA that owns the tile's first k-blocks (it reaches them last) adds the
+      // partials of the later segments, in k order, before its own epilogue.
+      int sk_others = 0;
+      if (CTAS == 1 && p.sk_per > 0) {
+        if (sg.kb0 > 0) {
+          float* mine = p.sk_partials + static_cast<size_t>(unit) * (ACC_COLS * BM);
+#pragma unroll 1
+          for (int c = 0; c < ACC_COLS / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_acc + c * 32, r);
+            tmem_ld_wait();
+            if (row < p.M) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) mine[(c * 32 + j) * BM + row_in_tile] = __uint_as_float(r[j]);
+            }
+          }
+          tc_fence_before();
+          mbar_arrive(&tempty[acc]);
+          __threadfence();
+          epilogue_bar_sync();
+          if (threadIdx.x == 4 * 32) atomicAdd(p.sk_counters + t, 1u);
+          continue;
+        }
+        if (sg.kb1 < p.num_kb) {
+          // number of later CTAs that hold k-blocks of this tile
+          const long long last_unit = static_cast<long long>(t + 1) * p.num_kb - 1;
+          sk_others = static_cast<int>(last_unit / p.sk_per) - unit;
+          if (threadIdx.x == 4 * 32) {
+            uint32_t spins = 0;
+            while (ld_acquire_gpu(p.sk_counters + t) < static_cast<unsigned>(sk_others)) {
+              if ((++spins & 0xffu) == 0u) {
+                if (*dl.abort) break;
+                if (globaltimer_ns() > dl.t_end) {
+                  *dl.abort = 1u;
+                  report(dl.status, 1u, WHERE_SK_PARTIALS, static_cast<unsigned>(t));
+                  break;
+                }
+              }
+            }
+          }
+          epilogue_bar_sync();
+          if (*dl.abort) break;
+          // fold the partial sums into the accumulator in tensor memory, 32 columns at a time;
+          // the epilogue below then runs unchanged
+#pragma unroll 1
+          for (int c = 0; c < ACC_COLS / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_acc + c * 32, r);
+            tmem_ld_wait();
+            if (row < p.M) {
+#pragma unroll 2
+              for (int o2 = 1; o2 <= sk_others; ++o2) {
+                const float* part = p.sk_partials + static_cast<size_t>(unit + o2) * (ACC_COLS * BM) + row_in_tile;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(part + (c * 32 + j) * BM));
+              }
+            }
+            tmem_st_32x32(t_acc + c * 32, r);
+            tmem_st_wait();
+          }
+        }
+      }
 
       if (MODE == MODE_GATEUP) {
 #pragma unroll 1
@@ -426,9 +559,16 @@ static int max_active_pairs() {
   return n;
 }
 
+constexpr size_t kSkCounterBytes = 8192;                      // up to 2048 tiles
+constexpr size_t kSkPartialBytes = size_t(ACC_COLS) * BM * 4;  // one 128 x 256 fp32 tile per CTA
+
+static size_t splitk_workspace_bytes_for(int sms) {
+  return kSkCounterBytes + static_cast<size_t>(sms) * kSkPartialBytes;
+}
+
 template <int MODE, int CTAS>
 static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b0, const CUtensorMap& tm_b1, GemmParams p,
-                          int max_ctas, int sms, cudaStream_t stream) {
+                          int max_ctas, int sms, void* sk_ws, size_t sk_ws_bytes, cudaStream_t stream) {
   using Cfg = TileCfg<CTAS>;
   constexpr int BN_OUT = (MODE == MODE_GATEUP) ? 128 : 256;
   // the attribute is per device; setting it on every call is cheap and covers every device that launches
@@ -446,11 +586,37 @@ static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b0, con
   if (units <= 0) units = sms / CTAS;
   if (max_ctas > 0 && max_ctas / CTAS < units) units = max_ctas / CTAS;
   if (units < 1) units = 1;
-  if (p.num_tiles < units) units = p.num_tiles;
+  // Stream-K when whole tiles would leave more than 40 % of the SMs idle and the caller provided
+  // scratch for the partial sums. (At 112 tiles on 148 SMs it measured slower than whole tiles.)
+  p.sk_per = 0;
+  p.sk_partials = nullptr;
+  p.sk_counters = nullptr;
+  if (CTAS == 1 && sk_ws != nullptr && tuning_int("DF_GEMM_STREAMK", 1) != 0) {
+    const int waves = (p.num_tiles + units - 1) / units;
+    const double eff = static_cast<double>(p.num_tiles) / (static_cast<double>(waves) * units);
+    const long long total = static_cast<long long>(p.num_tiles) * p.num_kb;
+    if (eff < 0.6 && p.num_tiles <= units && p.num_kb >= 8 &&
+        static_cast<size_t>(p.num_tiles) * 4 <= kSkCounterBytes) {
+      long long g = units;
+      if (g > total / 4) g = total / 4;  // at least four k-blocks per CTA
+      if (g < 1) g = 1;
+      const long long per = (total + g - 1) / g;
+      const long long grid = (total + per - 1) / per;
+      if (kSkCounterBytes + static_cast<size_t>(grid) * kSkPartialBytes <= sk_ws_bytes) {
+        p.sk_per = static_cast<int>(per);
+        p.sk_counters = static_cast<unsigned int*>(sk_ws);
+        p.sk_partials = reinterpret_cast<float*>(static_cast<uint8_t*>(sk_ws) + kSkCounterBytes);
+        units = static_cast<int>(grid);
+        cudaError_t me = cudaMemsetAsync(p.sk_counters, 0, static_cast<size_t>(p.num_tiles) * 4, stream);
+        if (me != cudaSuccess) return fail(DF_ECUDA, "stream-K counter reset: %s", cudaGetErrorString(me));
+      }
+    }
+  }
+  if (p.sk_per == 0 && p.num_tiles < units) units = p.num_tiles;
 
   if (tuning_int("DF_DEBUG", 0) > 0)
-    std::fprintf(stderr, "[df] gemm mode=%d ctas=%d M=%d N=%d K=%d tiles=%d grid=%d group_m=%d\n", MODE, CTAS, p.M, p.N,
-                 p.K, p.num_tiles, units * CTAS, p.group_m);
+    std::fprintf(stderr, "[df] gemm mode=%d ctas=%d M=%d N=%d K=%d tiles=%d grid=%d group_m=%d streamk_per=%d\n", MODE,
+                 CTAS, p.M, p.N, p.K, p.num_tiles, units * CTAS, p.group_m, p.sk_per);
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(units * CTAS, 1, 1);
@@ -474,7 +640,7 @@ static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b0, con
 
 template <int MODE>
 static int launch_gemm(const void* a, const void* b0, const void* b1, void* c, int M, int N, int K, int lda, int ldb,
-                       int ldc, int max_ctas, df_status_t* dev_status, void* stream) {
+                       int ldc, int max_ctas, void* sk_ws, size_t sk_ws_bytes, df_status_t* dev_status, void* stream) {
   if (a == nullptr || b0 == nullptr || b1 == nullptr || c == nullptr || dev_status == nullptr)
     return fail(DF_EINVAL, "NULL pointer argument");
   if (M <= 0 || N <= 0 || K <= 0) return fail(DF_EINVAL, "M, N, K must be positive (got %d, %d, %d)", M, N, K);
@@ -483,6 +649,8 @@ static int launch_gemm(const void* a, const void* b0, const void* b1, void* c, i
     return fail(DF_EINVAL, "leading dimensions must cover the row and be multiples of 8");
   if (!aligned16(a) || !aligned16(b0) || !aligned16(b1) || !aligned16(c))
     return fail(DF_EINVAL, "matrix base pointers must be 16-byte aligned");
+  if (sk_ws != nullptr && (reinterpret_cast<uintptr_t>(sk_ws) & 255u) != 0)
+    return fail(DF_EINVAL, "the stream-K workspace must be 256-byte aligned");
 
   int sms = df_sm_count();
   if (sms <= 0) return fail(DF_ECUDA, "no CUDA device");
@@ -502,6 +670,9 @@ static int launch_gemm(const void* a, const void* b0, const void* b1, void* c, i
   p.C = static_cast<__nv_bfloat16*>(c);
   p.status = reinterpret_cast<Status*>(dev_status);
   p.tiles_m = p.tiles_n = p.num_tiles = p.group_m = 0;
+  p.sk_per = 0;
+  p.sk_partials = nullptr;
+  p.sk_counters = nullptr;
   p.debug = tuning_int("DF_GEMM_DEBUG", 0);
 
   // One CTA per tile is the default: measured on B200 under the power cap, the CTA-pair
@@ -510,8 +681,10 @@ static int launch_gemm(const void* a, const void* b0, const void* b1, void* c, i
   // DF_GEMM_CTAS=2 selects the pair variant.
   const int want = tuning_int("DF_GEMM_CTAS", 1);
   const bool two = want == 2 && M > BM && (max_ctas <= 0 || max_ctas >= 2);
-  if (two) return launch_variant<MODE, 2>(tm_a, tm_b0, tm_b1, p, max_ctas, sms, static_cast<cudaStream_t>(stream));
-  return launch_variant<MODE, 1>(tm_a, tm_b0, tm_b1, p, max_ctas, sms, static_cast<cudaStream_t>(stream));
+  if (two)
+    return launch_variant<MODE, 2>(tm_a, tm_b0, tm_b1, p, max_ctas, sms, nullptr, 0, static_cast<cudaStream_t>(stream));
+  return launch_variant<MODE, 1>(tm_a, tm_b0, tm_b1, p, max_ctas, sms, sk_ws, sk_ws_bytes,
+                                 static_cast<cudaStream_t>(stream));
 }
 
 }  // namespace df
@@ -520,29 +693,55 @@ extern "C" {
 
 int df_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int lda, int ldb, int ldc, int max_ctas,
                  df_status_t* dev_status, void* stream) {
-  return df::launch_gemm<df::MODE_PLAIN>(a, b, b, c, M, N, K, lda, ldb, ldc, max_ctas, dev_status, stream);
+  return df::launch_gemm<df::MODE_PLAIN>(a, b, b, c, M, N, K, lda, ldb, ldc, max_ctas, nullptr, 0, dev_status, stream);
+}
+
+int df_gemm_bf16_ws(const void* a, const void* b, void* c, int M, int N, int K, int lda, int ldb, int ldc, int max_ctas,
+                    void* splitk_ws, size_t splitk_ws_bytes, df_status_t* dev_status, void* stream) {
+  return df::launch_gemm<df::MODE_PLAIN>(a, b, b, c, M, N, K, lda, ldb, ldc, max_ctas, splitk_ws, splitk_ws_bytes,
+                                         dev_status, stream);
 }
 
 int df_gateup_silu_bf16(const void* x, const void* w_gate, const void* w_up, void* h, int M, int H, int I, int ldx,
                         int ldw, int ldh, int max_ctas, df_status_t* dev_status, void* stream) {
-  return df::launch_gemm<df::MODE_GATEUP>(x, w_gate, w_up, h, M, I, H, ldx, ldw, ldh, max_ctas, dev_status, stream);
+  return df::launch_gemm<df::MODE_GATEUP>(x, w_gate, w_up, h, M, I, H, ldx, ldw, ldh, max_ctas, nullptr, 0, dev_status,
+                                          stream);
+}
+
+int df_gateup_silu_bf16_ws(const void* x, const void* w_gate, const void* w_up, void* h, int M, int H, int I, int ldx,
+                           int ldw, int ldh, int max_ctas, void* splitk_ws, size_t splitk_ws_bytes,
+                           df_status_t* dev_status, void* stream) {
+  return df::launch_gemm<df::MODE_GATEUP>(x, w_gate, w_up, h, M, I, H, ldx, ldw, ldh, max_ctas, splitk_ws,
+                                          splitk_ws_bytes, dev_status, stream);
+}
+
+size_t df_gemm_splitk_workspace_bytes(void) {
+  const int sms = df_sm_count();
+  return df::splitk_workspace_bytes_for(sms > 0 ? sms : 148);
+}
+
+static size_t mlp_h_bytes(int M, int I) {
+  const size_t h_bytes = static_cast<size_t>(M) * static_cast<size_t>(I) * 2u;
+  return ((h_bytes + 255u) / 256u) * 256u + 256u;
 }
 
 size_t df_mlp_workspace_bytes(int M, int H, int I) {
   (void)H;
   if (M <= 0 || I <= 0) return 0;
-  const size_t h_bytes = static_cast<size_t>(M) * static_cast<size_t>(I) * 2u;
-  return ((h_bytes + 255u) / 256u) * 256u + 256u;
+  return mlp_h_bytes(M, I) + df_gemm_splitk_workspace_bytes();
 }
 
 int df_mlp_gated_bf16(const void* x, const void* w_gate, const void* w_up, const void* w_down, void* out,
                       void* workspace, int M, int H, int I, int max_ctas, df_status_t* dev_status, void* stream) {
   if (workspace == nullptr) return df::fail(DF_EINVAL, "workspace is NULL");
   if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return df::fail(DF_EINVAL, "workspace must be 256-byte aligned");
+  if (M <= 0 || I <= 0) return df::fail(DF_EINVAL, "M and I must be positive");
   void* h = workspace;
-  int r = df_gateup_silu_bf16(x, w_gate, w_up, h, M, H, I, H, H, I, max_ctas, dev_status, stream);
+  void* sk = static_cast<uint8_t*>(workspace) + mlp_h_bytes(M, I);
+  const size_t sk_bytes = df_gemm_splitk_workspace_bytes();
+  int r = df_gateup_silu_bf16_ws(x, w_gate, w_up, h, M, H, I, H, H, I, max_ctas, sk, sk_bytes, dev_status, stream);
   if (r != DF_OK) return r;
-  return df_gemm_bf16(h, w_down, out, M, H, I, I, I, H, max_ctas, dev_status, stream);
+  return df_gemm_bf16_ws(h, w_down, out, M, H, I, I, I, H, max_ctas, sk, sk_bytes, dev_status, stream);
 }
 
 }  // extern "C"

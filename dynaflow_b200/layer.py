@@ -81,14 +81,16 @@ class TensorParallelGatedMLP:
         return marks
 
     def forward_device(self, x: torch.Tensor, out: torch.Tensor, cuts: list[int], record_kernel_events: bool = False,
-                       results: list | None = None):
+                       results: list | None = None, skip_comm: bool = False, skip_compute: bool = False):
         """Runs ``mlp(x[cuts[i]:cuts[i+1]])`` for every micro-batch ``i`` on the current stream.
 
         Single rank: the rows land in ``out``. Tensor parallel: each micro-batch's partial
         output is written straight into the communicator's region and reduced on the
         communication stream while the next micro-batch's GEMMs run; the reduced rows
         are then ``comm.result(slot, rows)`` (appended to ``results`` if given), and the
-        current stream waits for the last reduction before the call returns."""
+        current stream waits for the last reduction before the call returns.
+        ``skip_comm`` / ``skip_compute`` run the same schedule with the reductions, resp. the
+        GEMMs, left out (measurement of how much communication the overlap hides)."""
         marks = []
         main = torch.cuda.current_stream(self.device)
         for mb in range(len(cuts) - 1):
@@ -97,10 +99,11 @@ class TensorParallelGatedMLP:
                 continue
             slot = mb % self.micro_batches
             target = out[lo:hi] if self.world == 1 else self.comm.partial(slot, hi - lo)
-            m = self._mlp(x[lo:hi], target, slot, record_kernel_events)
-            if m is not None:
-                marks.append(m)
-            if self.world > 1:
+            if not skip_compute:
+                m = self._mlp(x[lo:hi], target, slot, record_kernel_events)
+                if m is not None:
+                    marks.append(m)
+            if self.world > 1 and not skip_comm:
                 ready = torch.cuda.Event()
                 ready.record(main)
                 self.comm.stream.wait_event(ready)

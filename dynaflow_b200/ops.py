@@ -87,6 +87,22 @@ def _require_bf16_2d(name: str, t: torch.Tensor) -> None:
                          f"{t.dtype} {tuple(t.shape)} strides {t.stride()}")
 
 
+_splitk_ws: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def splitk_workspace(device: torch.device) -> torch.Tensor:
+    """Scratch for the stream-K form of the GEMMs: one per (device, stream), created on first
+    use, so that launches on different streams never share partial sums."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, torch.cuda.current_stream(device).cuda_stream)
+    ws = _splitk_ws.get(key)
+    if ws is None:
+        with torch.cuda.device(idx):
+            ws = torch.empty(int(_native.load().df_gemm_splitk_workspace_bytes()), dtype=torch.uint8, device=device)
+        _splitk_ws[key] = ws
+    return ws
+
+
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, max_ctas: int = 0) -> torch.Tensor:
     """``out[M,N] = a[M,K] @ b[N,K].T`` (``b`` in ``nn.Linear`` layout)."""
     _require_bf16_2d("a", a)
@@ -104,9 +120,11 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
         return out
     _dev_index(a)
     st = status_block(a.device)
-    rc = _native.load().df_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
-                                     out.stride(0), max_ctas, st.data_ptr(), _stream_ptr(a))
-    _check(rc, "df_gemm_bf16")
+    ws = splitk_workspace(a.device)
+    rc = _native.load().df_gemm_bf16_ws(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0),
+                                        out.stride(0), max_ctas, ws.data_ptr(), ws.numel(), st.data_ptr(),
+                                        _stream_ptr(a))
+    _check(rc, "df_gemm_bf16_ws")
     return out
 
 
@@ -127,10 +145,11 @@ def gateup_silu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, out: 
         return out
     _dev_index(x)
     st = status_block(x.device)
-    rc = _native.load().df_gateup_silu_bf16(x.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), out.data_ptr(), M, H, I,
-                                            x.stride(0), w_gate.stride(0), out.stride(0), max_ctas, st.data_ptr(),
-                                            _stream_ptr(x))
-    _check(rc, "df_gateup_silu_bf16")
+    ws = splitk_workspace(x.device)
+    rc = _native.load().df_gateup_silu_bf16_ws(x.data_ptr(), w_gate.data_ptr(), w_up.data_ptr(), out.data_ptr(), M, H, I,
+                                               x.stride(0), w_gate.stride(0), out.stride(0), max_ctas, ws.data_ptr(),
+                                               ws.numel(), st.data_ptr(), _stream_ptr(x))
+    _check(rc, "df_gateup_silu_bf16_ws")
     return out
 
 

@@ -100,8 +100,25 @@ int df_gemm_bf16(const void* a, const void* b, void* c, int M, int N, int K, int
 int df_gateup_silu_bf16(const void* x, const void* w_gate, const void* w_up, void* h, int M, int H, int I,
                         int ldx, int ldw, int ldh, int max_ctas, df_status_t* dev_status, void* stream);
 
-/* Bytes of scratch df_mlp_gated_bf16 needs for the bf16 intermediate h[M,I]
- * plus its tile-ready counters. */
+/* Small-M forms of the two GEMMs. With fewer output tiles than SMs (decode-sized
+ * nano-batches) the launch is bound by streaming the weights from HBM, so the
+ * k-blocks of all tiles are divided evenly over the SMs ("stream-K"): CTAs that
+ * only hold a tile's later k-blocks leave fp32 partial sums in `splitk_ws`, the
+ * CTA holding its first k-blocks adds them in k order (deterministic) and runs
+ * the epilogue. `splitk_ws` is caller-owned device scratch of at least
+ * df_gemm_splitk_workspace_bytes() bytes, 256-byte aligned, contents arbitrary;
+ * launches that can overlap on the GPU need separate workspaces. With
+ * splitk_ws == NULL, or when whole tiles already fill the SMs, these behave
+ * exactly like df_gemm_bf16 / df_gateup_silu_bf16. */
+size_t df_gemm_splitk_workspace_bytes(void);
+int df_gemm_bf16_ws(const void* a, const void* b, void* c, int M, int N, int K, int lda, int ldb, int ldc,
+                    int max_ctas, void* splitk_ws, size_t splitk_ws_bytes, df_status_t* dev_status, void* stream);
+int df_gateup_silu_bf16_ws(const void* x, const void* w_gate, const void* w_up, void* h, int M, int H, int I,
+                           int ldx, int ldw, int ldh, int max_ctas, void* splitk_ws, size_t splitk_ws_bytes,
+                           df_status_t* dev_status, void* stream);
+
+/* Bytes of scratch df_mlp_gated_bf16 needs: the bf16 intermediate h[M,I] plus one
+ * stream-K workspace. */
 size_t df_mlp_workspace_bytes(int M, int H, int I);
 
 /* out = (silu(x * w_gate^T) (.) (x * w_up^T)) * w_down^T  for one nano-batch.
