@@ -13,6 +13,10 @@ Public surface and semantics follow the reference's ``dynaflow/manager.py``:
   cached config (``manager.py:161-190``) and merges per-nano-batch results by
   concatenation along dim 0, field by field for tuples (``manager.py:236-261``).
 
+Addition: with ``additional_config["whole_forward_graph"]`` the split forward of each
+split shape is captured once as a single multi-stream CUDA graph and replayed
+(``runtime/graph_schedule.py``).
+
 Differences: nothing is printed per forward (set ``DYNAFLOW_LOG=1`` to log the
 split config), the readable graph dump is only written when ``DYNAFLOW_DUMP_GRAPH``
 is set, and no asyncio event loop is created per forward.
@@ -32,6 +36,7 @@ from .executor.compiler import SubgraphCompiler
 from .interface import InputInfo, OpSchedulerBase, SplitConfig
 from .matching import split_graph, tag_graph
 from .runtime.engine import DynaFlowEngine
+from .runtime.graph_schedule import WholeForwardGraphs
 
 
 def _targets_without(gm: torch.fx.GraphModule, forbidden_tag: str) -> list[str]:
@@ -71,6 +76,7 @@ class DynaFlowManager:
         self.cached_config: SplitConfig | None = None
         self.scheduler: OpSchedulerBase | None = None
         self.engine: DynaFlowEngine | None = None
+        self.forward_graphs: WholeForwardGraphs | None = None
 
     def initialize(self, graph_module: torch.fx.GraphModule, config: DynaFlowConfig, scheduler: OpSchedulerBase,
                    example_inputs: list[Any]) -> None:
@@ -96,6 +102,17 @@ class DynaFlowManager:
                          cudagraph_targets=cudagraph_targets).run(*example_inputs)
         self.engine = DynaFlowEngine(self.graph_module, config)
         self.scheduler = scheduler
+        self.forward_graphs = None
+        if config.additional_config.get("whole_forward_graph", False):
+            engine = self.engine
+
+            def is_dynamic(idx: int) -> bool:
+                example = engine.placeholder_nodes[idx].meta.get("example_value", None)
+                return (isinstance(example, torch.Tensor) and example.dim() > 0
+                        and isinstance(example.shape[0], torch.SymInt))
+
+            self.forward_graphs = WholeForwardGraphs(self._forward_split, is_dynamic,
+                                                     config.additional_config.get("whole_forward_graph_keys"))
 
     def prepare(self, batch_size: int, num_tokens: list[int], is_dryrun: bool = False,
                 use_cudagraph: bool = False) -> SplitConfig:
@@ -126,6 +143,9 @@ class DynaFlowManager:
             try:
                 if not cfg.is_dryrun and cfg.num_nano_batches == 1 and cfg.allow_fallback:
                     return self.engine.execute_single_batch(cfg, args, kwargs)
+                if self.forward_graphs is not None and not cfg.is_dryrun and not cfg.use_cudagraph and not kwargs:
+                    engine = self.engine
+                    return self.forward_graphs.run(cfg, args, kwargs, lambda: engine.last_trace)
                 return self._forward_split(cfg, args, kwargs)
             finally:
                 self.cached_config = None

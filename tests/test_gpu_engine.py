@@ -133,3 +133,52 @@ def test_cudagraph_capture_and_replay_two_nano_batches(model, mixed):
     with pytest.raises(AssertionError, match="dry run"):
         with torch.inference_mode():
             host.compiled(ids6)
+
+
+def test_whole_forward_graph_replays_the_recorded_schedule(model):
+    """The policy runs live once per split shape, under stream capture; later forwards of that
+    shape are one graph launch and must give the same rows; a new shape captures again."""
+    import time
+
+    from dynaflow_b200 import ops
+
+    ids = llama_oracle.make_ids(6, 32, SHAPE.vocab, seed=5).cuda()
+    ids_b = llama_oracle.make_ids(6, 32, SHAPE.vocab, seed=6).cuda()
+    with torch.inference_mode():
+        want, want_b = model(ids), model(ids_b)
+
+    eager = Host(model, _policy(make_config()))
+    got_eager = eager.run((ids,), two_way([0, 3, 6])).clone()
+    eager_trace = [(n, b, s) for n, b, _st, s in eager.manager.engine.last_trace]
+
+    config = make_config(whole_forward_graph=True)
+    host = Host(model, _policy(config), config)
+    first = host.run((ids,), two_way([0, 3, 6])).clone()          # warm-up + capture + first replay
+    graphs = host.manager.forward_graphs
+    assert graphs is not None and graphs.captures == 1
+    second = host.run((ids_b,), two_way([0, 3, 6])).clone()        # replay with new inputs, no policy run
+    assert graphs.captures == 1
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(first, got_eager)                           # same kernels, same order
+    assert _rel(first, want) <= TOL and _rel(second, want_b) <= TOL
+    entry = next(iter(graphs._entries.values()))
+    assert [(n, b, s) for n, b, _st, s in entry.trace] == eager_trace   # the recorded routing
+    assert entry.replays == 2
+    third = host.run((ids,), two_way([0, 1, 6]))                   # another split shape: second capture
+    assert graphs.captures == 2 and _rel(third, want) <= TOL
+
+    # dispatch cost: eager split forward (policy + engine per operator) vs one graph launch
+    def avg_ms(h, n=30):
+        for _ in range(3):
+            h.run((ids,), two_way([0, 3, 6]))
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            h.run((ids,), two_way([0, 3, 6]))
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / n * 1e3
+
+    t_eager, t_graph = avg_ms(eager), avg_ms(host)
+    print(f"split forward, 2 layers, 2 nano-batches: eager dispatch {t_eager:.3f} ms, graph replay {t_graph:.3f} ms")
+    assert t_graph < t_eager
