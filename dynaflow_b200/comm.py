@@ -113,6 +113,9 @@ class PeerComm(_Regions):
         self._partials = [_bf16_view(self.local[s] + self.partial_off, max_rows, hidden, device) for s in range(slots)]
         self._sums = [_bf16_view(self.local[s] + self.sum_off, max_rows, hidden, device) for s in range(slots)]
         self.stream = torch.cuda.Stream(device=device)
+        # per-slot argument blocks of the plain all-reduce, built once (the launch path stays short)
+        self._plain_views = [self._view(rank, self.regions[s]) for s in range(slots)]
+        self._status_ptr = ops.status_block(device).data_ptr()
 
     def partial(self, slot: int, rows: int) -> torch.Tensor:
         """Where this rank's partial sums of micro-batch slot ``slot`` must be written."""
@@ -124,14 +127,14 @@ class PeerComm(_Regions):
 
     def all_reduce(self, slot: int, rows: int) -> torch.Tensor:
         """Launches on the current stream; returns ``result(slot, rows)``."""
-        view = self._view(self.rank, self.regions[slot])
-        st = ops.status_block(self.device)
-        _check(self.lib.df_allreduce_bf16(ctypes.byref(view), self.world, self.max_rows, self.hidden, rows, self.n_ctas,
-                                          st.data_ptr(), torch.cuda.current_stream(self.device).cuda_stream),
-               "df_allreduce_bf16")
+        rc = self.lib.df_allreduce_bf16(ctypes.byref(self._plain_views[slot]), self.world, self.max_rows, self.hidden,
+                                        rows, self.n_ctas, self._status_ptr,
+                                        torch.cuda.current_stream(self.device).cuda_stream)
+        if rc != 0:
+            _check(rc, "df_allreduce_bf16")
         self.launches += 1
         self.bytes_reduced += rows * self.hidden * 2
-        return self.result(slot, rows)
+        return self._sums[slot][:rows]
 
     def all_reduce_add_rmsnorm(self, slot: int, rows: int, residual: torch.Tensor | None, weight: torch.Tensor,
                                out: torch.Tensor, residual_out: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:

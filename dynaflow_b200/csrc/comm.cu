@@ -152,34 +152,37 @@ __global__ void __launch_bounds__(kCommThreads, 2) allreduce_kernel(const CommPa
     // ---- phase 1: reduce this rank's slice and push it to everyone
     const int lo = static_cast<int>(static_cast<long long>(p.T) * me.rank / W);
     const int hi = static_cast<int>(static_cast<long long>(p.T) * (me.rank + 1) / W);
+    // U 16-byte vectors per peer in flight per lane: NVLink round trips are a few microseconds,
+    // so the bytes in flight (CTAs x 8 warps x 32 lanes x U x 16 B per peer), not the issue
+    // rate, set the bandwidth. U x W = 16 loads per lane keeps the register count level.
+    constexpr int U = (W <= 2) ? 8 : (W <= 4 ? 4 : 2);
     for (int row = lo + row_first; row < hi; row += row_stride) {
       const size_t base = static_cast<size_t>(row) * p.H;
-      for (int v0 = lane; v0 < nvec; v0 += 64) {
-        const int v1 = v0 + 32;
-        const bool two = v1 < nvec;
-        uint4 a[W], b[W];
+      for (int v0 = lane; v0 < nvec; v0 += 32 * U) {
+        uint4 in[U][W];
 #pragma unroll
-        for (int r = 0; r < W; ++r) {
-          a[r] = __ldcg(reinterpret_cast<const uint4*>(me.partial[r] + base) + v0);
-          if (two) b[r] = __ldcg(reinterpret_cast<const uint4*>(me.partial[r] + base) + v1);
-        }
-        float sa[8] = {0, 0, 0, 0, 0, 0, 0, 0}, sb[8] = {0, 0, 0, 0, 0, 0, 0, 0}, f[8];
+        for (int u = 0; u < U; ++u) {
+          const int v = v0 + 32 * u;
+          if (v < nvec) {
 #pragma unroll
-        for (int r = 0; r < W; ++r) {
-          unpack8(a[r], f);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) sa[i] += f[i];
-          if (two) {
-            unpack8(b[r], f);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) sb[i] += f[i];
+            for (int r = 0; r < W; ++r) in[u][r] = __ldcg(reinterpret_cast<const uint4*>(me.partial[r] + base) + v);
           }
         }
-        const uint4 ya = pack8(sa), yb = pack8(sb);
 #pragma unroll
-        for (int r = 0; r < W; ++r) {
-          __stcg(reinterpret_cast<uint4*>(me.sum[r] + base) + v0, ya);
-          if (two) __stcg(reinterpret_cast<uint4*>(me.sum[r] + base) + v1, yb);
+        for (int u = 0; u < U; ++u) {
+          const int v = v0 + 32 * u;
+          if (v < nvec) {
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}, f[8];
+#pragma unroll
+            for (int r = 0; r < W; ++r) {  // rank order: every element is summed in the same order everywhere
+              unpack8(in[u][r], f);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) acc[i] += f[i];
+            }
+            const uint4 y = pack8(acc);
+#pragma unroll
+            for (int r = 0; r < W; ++r) __stcg(reinterpret_cast<uint4*>(me.sum[r] + base) + v, y);
+          }
         }
       }
     }
