@@ -117,6 +117,46 @@ class TensorParallelGatedMLP:
             main.wait_stream(self.comm.stream)
         return marks
 
+    def forward_chain(self, x: torch.Tensor, cuts: list[int], layers: int, norm_weight: torch.Tensor,
+                      residual: torch.Tensor, skip_comm: bool = False, skip_compute: bool = False) -> list[torch.Tensor]:
+        """``layers`` tensor-parallel MLP blocks back to back, the way a decoder runs them: for
+        every micro-batch ``x <- rmsnorm(allreduce(mlp(x)) + residual) * w`` with the fused
+        reduction kernel on the communication stream, so that the reduction of micro-batch
+        ``i`` runs under the GEMMs of micro-batch ``i+1`` -- of the same block or, for the last
+        micro-batch, of the next block. (All blocks share this object's weights; it exists to
+        measure the steady-state overlap.) Returns the per-micro-batch outputs."""
+        assert self.world > 1 and self.comm is not None
+        main = torch.cuda.current_stream(self.device)
+        comm_stream = self.comm.stream
+        n_mb = len(cuts) - 1
+        xs = [x[cuts[i]:cuts[i + 1]] for i in range(n_mb)]
+        res = [residual[cuts[i]:cuts[i + 1]] for i in range(n_mb)]
+        outs = [self.staging_out[i % self.micro_batches][: cuts[i + 1] - cuts[i]] for i in range(n_mb)]
+        start = torch.cuda.Event()
+        start.record(main)
+        comm_stream.wait_event(start)
+        reduced: list[torch.cuda.Event | None] = [None] * n_mb
+        for _layer in range(layers):
+            for mb in range(n_mb):
+                rows = cuts[mb + 1] - cuts[mb]
+                slot = mb % self.micro_batches
+                if reduced[mb] is not None:
+                    main.wait_event(reduced[mb])          # this micro-batch's input is the previous block's output
+                if not skip_compute:
+                    self._mlp(xs[mb], self.comm.partial(slot, rows), slot, False)
+                ready = torch.cuda.Event()
+                ready.record(main)
+                if not skip_comm:
+                    comm_stream.wait_event(ready)
+                    with torch.cuda.stream(comm_stream):
+                        self.comm.all_reduce_add_rmsnorm(slot, rows, res[mb], norm_weight, outs[mb], res[mb])
+                        done = torch.cuda.Event()
+                        done.record(comm_stream)
+                    reduced[mb] = done
+                    xs[mb] = outs[mb]
+        main.wait_stream(comm_stream)
+        return outs
+
     def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, cuts: list[int]) -> None:
         """Same step from pinned host memory: copy-in, GEMMs, reduction and copy-out of a
         micro-batch ride on that micro-batch's own stream."""

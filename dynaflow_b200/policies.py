@@ -175,3 +175,28 @@ class EqualSplitScheduler(_StreamedPolicy):
                     live.remove(b)
                 else:
                     await self._run(context, op)
+
+
+def agree_on_split(split_config: SplitConfig, batch_size: int, group: Any = None) -> tuple[SplitConfig, list[list[int]]]:
+    """Cross-rank agreement on the nano-batch split for data-parallel ranks that meet in a
+    collective inside the forward (expert parallelism): if any rank decided not to split, no
+    rank splits, since all ranks must issue the same number of collectives
+    (``examples/ae/patch/vllm.patch:598-632``). Host-side, CPU objects only.
+
+    Returns the possibly downgraded config and, per nano-batch, the padded row count of
+    every rank (what the reference packs into ``DPMetadata``, ``vllm.patch:634-664``)."""
+    import torch.distributed as dist
+
+    if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return split_config, [[n] for n in split_config.num_tokens_padded]
+    world = dist.get_world_size(group)
+    configs: list[Any] = [None] * world
+    dist.all_gather_object(configs, split_config, group=group)
+    if any(c.num_nano_batches == 1 for c in configs) and split_config.num_nano_batches != 1:
+        total, padded = sum(split_config.num_tokens), sum(split_config.num_tokens_padded)
+        split_config = SplitConfig(1, [batch_size], [0, batch_size], [total], [padded], [0, total],
+                                   is_dryrun=split_config.is_dryrun, use_cudagraph=False)
+    if any(c.num_nano_batches == 1 for c in configs):
+        dist.all_gather_object(configs, split_config, group=group)
+    rows = [[c.num_tokens_padded[i] for c in configs] for i in range(split_config.num_nano_batches)]
+    return split_config, rows
