@@ -137,7 +137,16 @@ class PeerComm(_Regions):
         return self._sums[slot][:rows]
 
     def all_reduce_add_rmsnorm(self, slot: int, rows: int, residual: torch.Tensor | None, weight: torch.Tensor,
-                               out: torch.Tensor, residual_out: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+                               out: torch.Tensor, residual_out: torch.Tensor, eps: float = 1e-5,
+                               fused: bool = True) -> torch.Tensor:
+        """``out = rmsnorm(allreduce(partial) + residual) * weight``; ``residual_out`` gets the sum.
+        ``fused=True``: one launch, the normalisation runs on the reduction's few CTAs.
+        ``fused=False``: the reduction, then the normalisation as a second launch over all SMs
+        (same bits; faster when the message is large)."""
+        if not fused:
+            y = self.all_reduce(slot, rows)
+            add_rmsnorm(y, residual, weight, out, residual_out, eps)
+            return out
         view = self._view(self.rank, self.regions[slot], residual, residual_out, out)
         st = ops.status_block(self.device)
         _check(self.lib.df_allreduce_add_rmsnorm_bf16(ctypes.byref(view), self.world, self.max_rows, self.hidden, rows,
@@ -161,6 +170,20 @@ class PeerComm(_Regions):
             for ptr in self.local:
                 self.lib.df_comm_region_free(ptr)
         self._opened, self.local = [], []
+
+
+def add_rmsnorm(y: torch.Tensor, residual: torch.Tensor | None, weight: torch.Tensor, out: torch.Tensor,
+                residual_out: torch.Tensor, eps: float = 1e-5) -> torch.Tensor:
+    """``r' = y + residual; out = rmsnorm(r') * weight; residual_out = r'`` on the current stream."""
+    T, H = y.shape
+    for t in (y, out, residual_out) + ((residual,) if residual is not None else ()):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous() or tuple(t.shape) != (T, H):
+            raise ValueError("add_rmsnorm takes contiguous bf16 [T, H] tensors")
+    rc = _native.load().df_add_rmsnorm_bf16(y.data_ptr(), residual.data_ptr() if residual is not None else None,
+                                            residual_out.data_ptr(), out.data_ptr(), weight.data_ptr(), eps, T, H,
+                                            torch.cuda.current_stream(y.device).cuda_stream)
+    _check(rc, "df_add_rmsnorm_bf16")
+    return out
 
 
 class EmulatedComm(_Regions):

@@ -47,6 +47,7 @@ constexpr int kCommThreads = 256;
 constexpr int kWarpsPerBlock = kCommThreads / 32;
 constexpr int kMaxCtas = DF_COMM_MAX_CTAS;
 constexpr unsigned WHERE_FLAG = 16;
+constexpr int kMaxSmemHidden = 8192;  // 16 KB of shared memory for the RMSNorm weight
 
 // Layout of a region (all offsets multiples of 256 bytes):
 //   [0, 4096)                         flag words: uint32 flags[2][kMaxCtas][kMaxWorld]
@@ -58,6 +59,8 @@ constexpr size_t kSeqOffset = kFlagBytes;
 constexpr size_t kHeaderBytes = 8192;
 
 static size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+
+enum : int { EPI_NONE = 0, EPI_ADD_RMSNORM = 1 };
 
 struct RankView {
   int rank;
@@ -79,7 +82,7 @@ struct CommParams {
   Status* status;
 };
 
-enum : int { EPI_NONE = 0, EPI_ADD_RMSNORM = 1 };
+
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -134,11 +137,102 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
   return v;
 }
 
-template <int W, bool EMULATE>
+// One row of r' = y + residual; out = bf16(r' * rsqrt(mean(r'^2) + eps)) * w, by one warp.
+// Each lane keeps kBatch vectors of the sum and of the residual in flight at a time
+// (explicit batches: the compiler may not move loads across the stores, the buffers can
+// alias). The new residual is read back for the second pass from this thread's own writes.
+__device__ __forceinline__ void add_rmsnorm_row(const __nv_bfloat16* y_base, const __nv_bfloat16* rin_base,
+                                                __nv_bfloat16* rout_base, __nv_bfloat16* out_base, const uint4* wv,
+                                                int row, int H, float eps, int lane) {
+  constexpr int kBatch = 8;
+  const int nvec = H >> 3;
+  const size_t base = static_cast<size_t>(row) * H;
+  const uint4* y = reinterpret_cast<const uint4*>(y_base + base);
+  const uint4* rin = rin_base != nullptr ? reinterpret_cast<const uint4*>(rin_base + base) : nullptr;
+  uint4* res_out = reinterpret_cast<uint4*>(rout_base + base);
+  uint4* o = reinterpret_cast<uint4*>(out_base + base);
+  float ss = 0.0f;
+  for (int v0 = lane; v0 < nvec; v0 += 32 * kBatch) {
+    uint4 yv[kBatch], rv[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int v = v0 + 32 * u;
+      if (v < nvec) {
+        yv[u] = __ldcg(y + v);
+        rv[u] = rin != nullptr ? rin[v] : make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int v = v0 + 32 * u;
+      if (v < nvec) {
+        float fy[8], fr[8];
+        unpack8(yv[u], fy);
+        unpack8(rv[u], fr);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) fy[i] += fr[i];
+        const uint4 packed = pack8(fy);
+        res_out[v] = packed;
+        unpack8(packed, fy);  // the sum of squares is taken over the rounded residual
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += fy[i] * fy[i];
+      }
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  const float inv = rsqrtf(ss / static_cast<float>(H) + eps);
+  for (int v0 = lane; v0 < nvec; v0 += 32 * kBatch) {
+    uint4 xv[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int v = v0 + 32 * u;
+      if (v < nvec) xv[u] = res_out[v];
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int v = v0 + 32 * u;
+      if (v < nvec) {
+        float fx[8], fw[8];
+        unpack8(xv[u], fx);
+        unpack8(wv[v], fw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) fx[i] = __bfloat162float(__float2bfloat16_rn(fx[i] * inv)) * fw[i];
+        o[v] = pack8(fx);
+      }
+    }
+  }
+}
+
+// Stand-alone residual add + RMSNorm over all SMs (one warp per row): the second half of the
+// fused reduction as its own launch, for when the reduction itself runs on few CTAs.
+__global__ void __launch_bounds__(kCommThreads) add_rmsnorm_kernel(const __nv_bfloat16* y, const __nv_bfloat16* rin,
+                                                                    __nv_bfloat16* rout, __nv_bfloat16* out,
+                                                                    const __nv_bfloat16* weight, int T, int H, float eps) {
+  extern __shared__ uint4 s_weight[];
+  const bool staged = H <= kMaxSmemHidden;
+  if (staged) {
+    for (int v = threadIdx.x; v < (H >> 3); v += blockDim.x) s_weight[v] = reinterpret_cast<const uint4*>(weight)[v];
+    __syncthreads();
+  }
+  const uint4* wv = staged ? s_weight : reinterpret_cast<const uint4*>(weight);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int row = blockIdx.x * kWarpsPerBlock + warp; row < T; row += gridDim.x * kWarpsPerBlock)
+    add_rmsnorm_row(y, rin, rout, out, wv, row, H, eps, lane);
+}
+
+template <int W, bool EMULATE, int EPI>
 __global__ void __launch_bounds__(kCommThreads, 2) allreduce_kernel(const CommParams p) {
   __shared__ uint32_t s_abort;
+  // RMSNorm weight staged once per CTA (EPI_ADD_RMSNORM, hidden <= kMaxSmemHidden): weight loads
+  // from global memory could not be moved across the output stores and cost one exposed L2
+  // round trip per vector.
+  extern __shared__ uint4 s_weight[];
   const RankView& me = p.ranks[EMULATE ? blockIdx.y : 0];
   if (threadIdx.x == 0) s_abort = 0u;
+  if (EPI == EPI_ADD_RMSNORM && p.H <= kMaxSmemHidden) {
+    for (int v = threadIdx.x; v < (p.H >> 3); v += blockDim.x) s_weight[v] = reinterpret_cast<const uint4*>(p.weight)[v];
+  }
   const unsigned long long t_end = globaltimer_ns() + p.timeout_ns;
   const uint32_t seq = me.seq[blockIdx.x];  // same value on every rank: one increment per launch
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -189,44 +283,15 @@ __global__ void __launch_bounds__(kCommThreads, 2) allreduce_kernel(const CommPa
     ok = peer_barrier(me, W, 1, seq, t_end, p.status, &s_abort);
   }
 
-  if (ok && p.mode == EPI_ADD_RMSNORM) {
+  if (EPI == EPI_ADD_RMSNORM && ok) {
     // ---- phase 2: residual add + RMSNorm of the rows the blocks with this index delivered
-    const float inv_h = 1.0f / static_cast<float>(p.H);
+    // (local memory traffic only).
+    const uint4* wv = (p.H <= kMaxSmemHidden) ? s_weight : reinterpret_cast<const uint4*>(p.weight);
     for (int q = 0; q < W; ++q) {
       const int lo = static_cast<int>(static_cast<long long>(p.T) * q / W);
       const int hi = static_cast<int>(static_cast<long long>(p.T) * (q + 1) / W);
-      for (int row = lo + row_first; row < hi; row += row_stride) {
-        const size_t base = static_cast<size_t>(row) * p.H;
-        const uint4* y = reinterpret_cast<const uint4*>(me.sum[me.rank] + base);
-        uint4* res_out = reinterpret_cast<uint4*>(me.residual_out + base);
-        float ss = 0.0f;
-        for (int v = lane; v < nvec; v += 32) {
-          float fy[8], fr[8];
-          unpack8(__ldcg(y + v), fy);
-          if (me.residual_in != nullptr) {
-            unpack8(reinterpret_cast<const uint4*>(me.residual_in + base)[v], fr);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) fy[i] += fr[i];
-          }
-          const uint4 packed = pack8(fy);
-          res_out[v] = packed;
-          unpack8(packed, fy);  // the sum of squares is taken over the rounded residual
-#pragma unroll
-          for (int i = 0; i < 8; ++i) ss += fy[i] * fy[i];
-        }
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
-        const float inv = rsqrtf(ss * inv_h + p.eps);
-        uint4* o = reinterpret_cast<uint4*>(me.out + base);
-        for (int v = lane; v < nvec; v += 32) {
-          float fx[8], fw[8];
-          unpack8(res_out[v], fx);
-          unpack8(reinterpret_cast<const uint4*>(p.weight)[v], fw);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) fx[i] = __bfloat162float(__float2bfloat16_rn(fx[i] * inv)) * fw[i];
-          o[v] = pack8(fx);
-        }
-      }
+      for (int row = lo + row_first; row < hi; row += row_stride)
+        add_rmsnorm_row(me.sum[me.rank], me.residual_in, me.residual_out, me.out, wv, row, p.H, p.eps, lane);
     }
   }
 
@@ -256,9 +321,11 @@ static int launch_allreduce(const CommParams& p, int n_ctas, int emulated, void*
   void* args[] = {const_cast<CommParams*>(&p)};
   const void* fn = nullptr;
   switch (p.world) {
-#define DF_CASE(W)                                                          \
-  case W:                                                                   \
-    fn = reinterpret_cast<const void*>(&allreduce_kernel<W, EMULATE>);      \
+#define DF_CASE(W)                                                                               \
+  case W:                                                                                        \
+    fn = (p.mode == EPI_ADD_RMSNORM)                                                             \
+             ? reinterpret_cast<const void*>(&allreduce_kernel<W, EMULATE, EPI_ADD_RMSNORM>)     \
+             : reinterpret_cast<const void*>(&allreduce_kernel<W, EMULATE, EPI_NONE>);           \
     break;
     DF_CASE(1) DF_CASE(2) DF_CASE(3) DF_CASE(4) DF_CASE(5) DF_CASE(6) DF_CASE(7) DF_CASE(8)
 #undef DF_CASE
@@ -266,11 +333,12 @@ static int launch_allreduce(const CommParams& p, int n_ctas, int emulated, void*
       return fail(DF_EUNSUPPORTED, "world size %d is outside [1, %d]", p.world, kMaxWorld);
   }
   cudaError_t e;
+  const size_t smem = (p.mode == EPI_ADD_RMSNORM && p.H <= kMaxSmemHidden) ? static_cast<size_t>(p.H) * 2 : 0;
   if (EMULATE) {
     // every emulated rank must be resident at once: its blocks wait on the others'
-    e = cudaLaunchCooperativeKernel(fn, grid, block, args, 0, static_cast<cudaStream_t>(stream));
+    e = cudaLaunchCooperativeKernel(fn, grid, block, args, smem, static_cast<cudaStream_t>(stream));
   } else {
-    e = cudaLaunchKernel(fn, grid, block, args, 0, static_cast<cudaStream_t>(stream));
+    e = cudaLaunchKernel(fn, grid, block, args, smem, static_cast<cudaStream_t>(stream));
   }
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
@@ -407,6 +475,29 @@ int df_allreduce_add_rmsnorm_bf16(const df_comm_rank_t* view, int world, int max
   int r = df::fill_params(&p, 1, view, world, max_rows, hidden, T, hidden, df::EPI_ADD_RMSNORM, weight, eps, dev_status);
   if (r != DF_OK) return r;
   return df::launch_allreduce<false>(p, df::clamp_ctas(n_ctas), 1, stream);
+}
+
+int df_add_rmsnorm_bf16(const void* y, const void* residual_in, void* residual_out, void* out, const void* weight,
+                        float eps, int T, int H, void* stream) {
+  if (y == nullptr || residual_out == nullptr || out == nullptr || weight == nullptr)
+    return df::fail(DF_EINVAL, "NULL pointer argument");
+  if (T <= 0 || H <= 0 || (H % 8) != 0) return df::fail(DF_EINVAL, "T must be positive and H a positive multiple of 8");
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(residual_in) |
+                         reinterpret_cast<uintptr_t>(residual_out) | reinterpret_cast<uintptr_t>(out) |
+                         reinterpret_cast<uintptr_t>(weight);
+  if (bits & 15u) return df::fail(DF_EINVAL, "pointers must be 16-byte aligned");
+  int sms = df_sm_count();
+  if (sms <= 0) return df::fail(DF_ECUDA, "no CUDA device");
+  int grid = (T + df::kWarpsPerBlock - 1) / df::kWarpsPerBlock;
+  if (grid > sms * 8) grid = sms * 8;
+  const size_t smem = H <= df::kMaxSmemHidden ? static_cast<size_t>(H) * 2 : 0;
+  df::add_rmsnorm_kernel<<<grid, df::kCommThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(residual_in),
+      static_cast<__nv_bfloat16*>(residual_out), static_cast<__nv_bfloat16*>(out),
+      static_cast<const __nv_bfloat16*>(weight), T, H, eps);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return df::fail(DF_ECUDA, "add_rmsnorm launch: %s", cudaGetErrorString(e));
+  return DF_OK;
 }
 
 int df_allreduce_emulated_bf16(const df_comm_rank_t* views, int world, int max_rows, int hidden, int T,

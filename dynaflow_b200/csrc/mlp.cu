@@ -398,7 +398,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             tmem_ld_32x32(t_acc + c * 32, r);
             tmem_ld_wait();
             if (row < p.M) {
-#pragma unroll 2
+#pragma unroll 1  // (unrolling costs 32 registers, which the co-resident reduction kernel needs)
               for (int o2 = 1; o2 <= sk_others; ++o2) {
                 const float* part = p.sk_partials + static_cast<size_t>(unit + o2) * (ACC_COLS * BM) + row_in_tile;
 #pragma unroll

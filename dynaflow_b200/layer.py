@@ -118,7 +118,8 @@ class TensorParallelGatedMLP:
         return marks
 
     def forward_chain(self, x: torch.Tensor, cuts: list[int], layers: int, norm_weight: torch.Tensor,
-                      residual: torch.Tensor, skip_comm: bool = False, skip_compute: bool = False) -> list[torch.Tensor]:
+                      residual: torch.Tensor, skip_comm: bool = False, skip_compute: bool = False,
+                      fused_norm: bool = True) -> list[torch.Tensor]:
         """``layers`` tensor-parallel MLP blocks back to back, the way a decoder runs them: for
         every micro-batch ``x <- rmsnorm(allreduce(mlp(x)) + residual) * w`` with the fused
         reduction kernel on the communication stream, so that the reduction of micro-batch
@@ -149,7 +150,8 @@ class TensorParallelGatedMLP:
                 if not skip_comm:
                     comm_stream.wait_event(ready)
                     with torch.cuda.stream(comm_stream):
-                        self.comm.all_reduce_add_rmsnorm(slot, rows, res[mb], norm_weight, outs[mb], res[mb])
+                        self.comm.all_reduce_add_rmsnorm(slot, rows, res[mb], norm_weight, outs[mb], res[mb],
+                                                         fused=fused_norm)
                         done = torch.cuda.Event()
                         done.record(comm_stream)
                     reduced[mb] = done

@@ -185,6 +185,15 @@ int df_allreduce_add_rmsnorm_bf16(const df_comm_rank_t* view, int world, int max
                                   const void* weight, float eps, int n_ctas, df_status_t* dev_status,
                                   void* stream);
 
+/* The second half of the fused call as its own launch over all SMs:
+ * r' = y + residual_in (NULL = zeros); out = bf16(r' * rsqrt(mean(r'^2) + eps)) * weight;
+ * residual_out = r' (may equal residual_in). The RMSNorm(+residual) module a host model
+ * runs after an all-reduce (matched together with it by
+ * examples/ae/scheduler/vllm/nanoflow.py:59-69). df_allreduce_bf16 followed by this on the
+ * result buffer equals df_allreduce_add_rmsnorm_bf16 bit for bit. */
+int df_add_rmsnorm_bf16(const void* y, const void* residual_in, void* residual_out, void* out, const void* weight,
+                        float eps, int T, int H, void* stream);
+
 /* Test vehicle: runs `world` ranks of the same kernel on ONE GPU as one cooperative
  * launch (grid.y = rank), `views[r]` describing rank r, all regions in this GPU's
  * memory. Exercises the flag protocol and the arithmetic without a second GPU.

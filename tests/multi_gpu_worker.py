@@ -75,6 +75,27 @@ def main() -> None:
     ops.check_status()
     assert torch.equal(out_host, got), f"rank {rank}: host-staged step differs from the device-resident one"
     dist.barrier()
+
+    # ---- two TP blocks back to back with the fused reduction + residual + RMSNorm between them
+    norm_w = (1 + 0.1 * torch.randn(H, generator=g)).bfloat16()
+    res0 = torch.randn(2 * T, H, generator=g).bfloat16()
+    res_dev = res0.to(dev)
+    outs = layer.forward_chain(x.to(dev), [0, T, 2 * T], 2, norm_w.to(dev), res_dev)
+    torch.cuda.synchronize()
+    ops.check_status()
+    xo, ro = x, res0
+    for _ in range(2):                          # oracle: shard, reduce in rank order, add, normalise
+        parts = []
+        for r in range(world):
+            lo, hi = r * (I // world), (r + 1) * (I // world)
+            parts.append(ops_oracle.gated_mlp(xo, w_gate[lo:hi], w_up[lo:hi], w_down[:, lo:hi]))
+        xo, ro = ops_oracle.allreduce_add_rmsnorm(parts, ro, norm_w)
+    got = torch.cat([o.cpu() for o in outs])
+    rel = ((got.float() - xo.float()).abs().max() / xo.float().abs().max()).item()
+    assert rel <= 2e-2, f"rank {rank}: chained TP blocks rel err {rel}"
+    rel = ((res_dev.cpu().float() - ro.float()).abs().max() / ro.float().abs().max()).item()
+    assert rel <= 2e-2, f"rank {rank}: chained residual rel err {rel}"
+    dist.barrier()
     comm.close()
     dist.destroy_process_group()
     if rank == 0:
