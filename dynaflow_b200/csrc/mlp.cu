@@ -57,7 +57,7 @@ struct TileCfg {
   static constexpr int kBBytes = (CTAS == 2) ? B_HALF_BYTES : 2 * B_HALF_BYTES;  // per CTA
   static constexpr int kStageBytes = A_BYTES + kBBytes;
   static constexpr int kTileM = BM * CTAS;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 512 /*barriers, tile ring*/;
 };
 
 enum : int { MODE_PLAIN = 0, MODE_GATEUP = 1 };
@@ -73,6 +73,10 @@ struct GemmParams {
   int sk_per;
   float* sk_partials;        // [grid][256 columns][128 rows] fp32, column-major per CTA
   unsigned int* sk_counters;  // [num_tiles] partial segments delivered, zero at launch
+  // Dynamic tile order (1-CTA whole-tile launches with a workspace): the first tile of a CTA is
+  // its block index, the next ones come from this counter (zero at launch), so a CTA that
+  // shares its SM with the reduction kernel of the other micro-batch simply takes fewer tiles.
+  unsigned int* tile_counter;
   int debug;  // development only: bit 0 = producer skips the copies, bit 1 = epilogue skips the stores
   unsigned long long timeout_ns;
   __nv_bfloat16* C;
@@ -104,15 +108,33 @@ struct Segment {
   int tile, kb0, kb1;
 };
 
-// The sequence of segments of a CTA. Data-parallel: whole tiles unit, unit + num_units, ...
+constexpr int kSchedSlots = 4;
+enum : int { ROLE_PRODUCER = 0, ROLE_MMA = 1, ROLE_EPILOGUE = 2 };
+
+// Hand-off of dynamically fetched tile indices from the producer warp to the MMA thread and
+// the epilogue warps: a small ring in shared memory guarded by two mbarriers per slot.
+struct SchedRing {
+  uint64_t* full;      // [kSchedSlots] one arrival: the producer published a tile index
+  uint64_t* empty;     // [kSchedSlots] five arrivals: MMA thread + four epilogue warps read it
+  volatile int* tile;  // [kSchedSlots] tile index, -1 = no more work
+  unsigned int* counter;
+};
+
+// The sequence of segments of a CTA. Static: whole tiles unit, unit + num_units, ...
+// Dynamic: whole tiles, the first one = unit, then whatever the global counter hands out.
 // Stream-K: the units [unit * sk_per, (unit + 1) * sk_per) of the tile-major k-block sequence,
 // cut at tile boundaries. All three warp roles walk the same sequence.
 struct SegmentIter {
-  int cur, end, step, num_kb;
-  bool streamk;
+  int cur, end, step, num_kb, num_tiles, iter, first, grid;
+  bool streamk, dynamic;
   __device__ SegmentIter(const GemmParams& p, int unit, int num_units) {
     num_kb = p.num_kb;
+    num_tiles = p.num_tiles;
     streamk = p.sk_per > 0;
+    dynamic = !streamk && p.tile_counter != nullptr;
+    iter = 0;
+    first = unit;
+    grid = num_units;
     if (streamk) {
       const long long total = static_cast<long long>(p.num_tiles) * p.num_kb;
       const long long b = static_cast<long long>(unit) * p.sk_per;
@@ -126,7 +148,39 @@ struct SegmentIter {
       step = num_units;
     }
   }
-  __device__ bool next(Segment& s) {
+  // ROLE_PRODUCER and ROLE_MMA: called by one thread. ROLE_EPILOGUE: by whole warps.
+  template <int ROLE>
+  __device__ bool next(Segment& s, const SchedRing& ring, const Deadline& dl, int lane) {
+    if (dynamic) {
+      const int slot = iter % kSchedSlots;
+      const uint32_t round = static_cast<uint32_t>(iter / kSchedSlots);
+      int t;
+      if (ROLE == ROLE_PRODUCER) {
+        t = (iter == 0) ? first : grid + static_cast<int>(atomicAdd(ring.counter, 1u));
+        if (t >= num_tiles) t = -1;
+        if (round > 0 && !mbar_wait(&ring.empty[slot], (round - 1u) & 1u, dl, 6u, static_cast<unsigned>(iter)))
+          return false;
+        ring.tile[slot] = t;
+        mbar_arrive(&ring.full[slot]);  // release: the index is visible to whoever sees the arrival
+      } else {
+        bool ok = mbar_wait(&ring.full[slot], round & 1u, dl, 6u, static_cast<unsigned>(iter));
+        if (ROLE == ROLE_EPILOGUE) ok = __all_sync(0xffffffffu, ok);
+        if (!ok) return false;
+        t = ring.tile[slot];
+        if (ROLE == ROLE_MMA) {
+          mbar_arrive(&ring.empty[slot]);
+        } else {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ring.empty[slot]);
+        }
+      }
+      ++iter;
+      if (t < 0) return false;
+      s.tile = t;
+      s.kb0 = 0;
+      s.kb1 = num_kb;
+      return true;
+    }
     if (cur >= end) return false;
     if (streamk) {
       s.tile = cur / num_kb;
@@ -164,8 +218,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* sched_full = tempty + 2;
+  uint64_t* sched_empty = sched_full + kSchedSlots;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sched_empty + kSchedSlots);
   volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile int* sched_tile = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  const SchedRing ring{sched_full, sched_empty, sched_tile, p.tile_counter};
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -181,6 +239,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull[a], 1);
       mbar_init(&tempty[a], (CTAS == 2) ? 8 : 128);  // CTAS == 2: one arrival per epilogue warp of both CTAs
+    }
+    for (int i = 0; i < kSchedSlots; ++i) {
+      mbar_init(&sched_full[i], 1);
+      mbar_init(&sched_empty[i], 5);
     }
     *abort_flag = 0u;
     mbar_fence_init();
@@ -210,28 +272,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer
-    // Lane 0 issues the tile copies. (Prefetching operand boxes or weight-row chunks into L2
-    // ahead of the copies was measured and made every shape slower, by 20 % to 3x.)
-    int stage = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    SegmentIter segs(p, unit, num_units);
-    Segment sg;
-    while (ok && segs.next(sg)) {
-      const int t = sg.tile;
-      int m_blk, n_blk;
-      tile_coords(p, t, m_blk, n_blk);
-      const int m0 = m_blk * Cfg::kTileM + static_cast<int>(cta_rank) * BM;
-      const int n0 = n_blk * BN_OUT;
-      const int y1_1cta = (MODE == MODE_GATEUP) ? n0 : n0 + 128;
-
-      for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
-        if (lane == 0) {
-          if (!mbar_wait(&empty[stage], phase ^ 1u, dl, WHERE_PRODUCER, t)) ok = false;
-        }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) break;
-        if (lane == 0) {
+    // (Prefetching operand boxes or weight-row chunks into L2 ahead of the copies was measured
+    // and made every shape slower, by 20 % to 3x.)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      SegmentIter segs(p, unit, num_units);
+      Segment sg;
+      while (ok && segs.next<ROLE_PRODUCER>(sg, ring, dl, 0)) {
+        const int t = sg.tile;
+        int m_blk, n_blk;
+        tile_coords(p, t, m_blk, n_blk);
+        const int m0 = m_blk * Cfg::kTileM + static_cast<int>(cta_rank) * BM;
+        const int n0 = n_blk * BN_OUT;
+        const int y1_1cta = (MODE == MODE_GATEUP) ? n0 : n0 + 128;
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, dl, WHERE_PRODUCER, t)) {
+            ok = false;
+            break;
+          }
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           if (p.debug & 1) {
@@ -253,10 +313,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             tma_load_2d(sb, &tm_b0, &full[stage], kb * BK, n0);
             tma_load_2d(sb + B_HALF_BYTES, map1, &full[stage], kb * BK, y1_1cta);
           }
-        }
-        if (++stage == STAGES) {
-          stage = 0;
-          phase ^= 1u;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
         }
       }
     }
@@ -271,7 +331,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       bool ok = true;
       SegmentIter segs(p, unit, num_units);
       Segment sg;
-      for (; ok && segs.next(sg); ++it) {
+      for (; ok && segs.next<ROLE_MMA>(sg, ring, dl, 0); ++it) {
         const int t = sg.tile;
         const int acc = it & 1;
         const uint32_t aphase = (it >> 1) & 1u;
@@ -330,7 +390,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     int it = 0;
     SegmentIter segs(p, unit, num_units);
     Segment sg;
-    for (; segs.next(sg); ++it) {
+    for (; segs.next<ROLE_EPILOGUE>(sg, ring, dl, lane); ++it) {
       const int t = sg.tile;
       int m_blk, n_blk;
       tile_coords(p, t, m_blk, n_blk);
@@ -596,7 +656,7 @@ static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b0, con
     const double eff = static_cast<double>(p.num_tiles) / (static_cast<double>(waves) * units);
     const long long total = static_cast<long long>(p.num_tiles) * p.num_kb;
     if (eff < 0.6 && p.num_tiles <= units && p.num_kb >= 8 &&
-        static_cast<size_t>(p.num_tiles) * 4 <= kSkCounterBytes) {
+        static_cast<size_t>(p.num_tiles) * 4 <= kSkCounterBytes - 64) {
       long long g = units;
       if (g > total / 4) g = total / 4;  // at least four k-blocks per CTA
       if (g < 1) g = 1;
@@ -613,6 +673,14 @@ static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b0, con
     }
   }
   if (p.sk_per == 0 && p.num_tiles < units) units = p.num_tiles;
+  // whole tiles, more than one per CTA: hand them out dynamically
+  p.tile_counter = nullptr;
+  if (CTAS == 1 && p.sk_per == 0 && sk_ws != nullptr && sk_ws_bytes >= kSkCounterBytes && p.num_tiles > units &&
+      tuning_int("DF_GEMM_DYNAMIC", 1) != 0) {
+    p.tile_counter = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(sk_ws) + kSkCounterBytes - 64);
+    cudaError_t me = cudaMemsetAsync(p.tile_counter, 0, 4, stream);
+    if (me != cudaSuccess) return fail(DF_ECUDA, "tile counter reset: %s", cudaGetErrorString(me));
+  }
 
   if (tuning_int("DF_DEBUG", 0) > 0)
     std::fprintf(stderr, "[df] gemm mode=%d ctas=%d M=%d N=%d K=%d tiles=%d grid=%d group_m=%d streamk_per=%d\n", MODE,
@@ -673,6 +741,7 @@ static int launch_gemm(const void* a, const void* b0, const void* b1, void* c, i
   p.sk_per = 0;
   p.sk_partials = nullptr;
   p.sk_counters = nullptr;
+  p.tile_counter = nullptr;
   p.debug = tuning_int("DF_GEMM_DEBUG", 0);
 
   // One CTA per tile is the default: measured on B200 under the power cap, the CTA-pair
