@@ -161,10 +161,12 @@ class TensorParallelGatedMLP:
 
     def forward_host(self, x_host: torch.Tensor, out_host: torch.Tensor, cuts: list[int]) -> None:
         """Same step from pinned host memory: copy-in, GEMMs, reduction and copy-out of a
-        micro-batch ride on that micro-batch's own stream."""
+        micro-batch ride on that micro-batch's own stream. ``x_host`` must be complete on the
+        host when this is called (the copies do not wait for the caller's stream); the caller's
+        stream waits for both micro-batches' copy-out before anything it enqueues afterwards.
+        Consecutive calls pipeline: the copies of one micro-batch slot run under the GEMMs of
+        the other slot, across calls too."""
         main = torch.cuda.current_stream(self.device)
-        fork = torch.cuda.Event()
-        fork.record(main)
         joins = []
         for mb in range(len(cuts) - 1):
             lo, hi = cuts[mb], cuts[mb + 1]
@@ -172,7 +174,6 @@ class TensorParallelGatedMLP:
                 continue
             slot = mb % self.micro_batches
             stream = self.streams[slot]
-            stream.wait_event(fork)
             with torch.cuda.stream(stream):
                 xin = self.staging_in[slot][: hi - lo]
                 xin.copy_(x_host[lo:hi], non_blocking=True)
