@@ -200,3 +200,72 @@ def agree_on_split(split_config: SplitConfig, batch_size: int, group: Any = None
         dist.all_gather_object(configs, split_config, group=group)
     rows = [[c.num_tokens_padded[i] for c in configs] for i in range(split_config.num_nano_batches)]
     return split_config, rows
+
+
+class DBOScheduler(_StreamedPolicy):
+    """Dual-batch overlap for MoE layers: a hand-written interleaving that puts the dispatch and
+    combine all-to-alls of one nano-batch under the attention and expert GEMMs of the other
+    (``examples/ae/scheduler/vllm/dbo.py``). Framework-free restatement: subgraphs are recognised
+    by the tags ``attention`` / ``dispatch`` / ``expert`` / ``combine`` that the subclass's tag
+    rules assign; ``network``-tagged operators go to the communication stream.
+    ``before_execute(batch_idx, op)`` is called ahead of every operator, for hosts that keep
+    per-nano-batch state (attention / data-parallel metadata) in a global context
+    (``dbo.py:213-217``)."""
+
+    WARM_UP = (("attention", 0),)
+    SEQUENCE = (("attention", 1), ("dispatch", 0), ("expert", 0), ("dispatch", 1), ("expert", 1),
+                ("combine", 0), ("attention", 0), ("combine", 1))
+
+    def __init__(self, config: DynaFlowConfig, split_rules: list[MatchingRule] | None = None,
+                 tag_rules: dict[MatchingRule, set[str]] | None = None) -> None:
+        super().__init__(config, "dbo", split_rules, tag_rules)
+        self.min_nano_split_tokens = config.additional_config["min_nano_split_tokens"]
+        self.max_num_nano_batches = config.max_num_splits
+        self.cudagraph_capture_sizes = config.cudagraph_config.capture_sizes
+        self._splitter = NanoFlowScheduler.get_split_config  # same balanced two-way split (dbo.py:94-148)
+
+    def get_split_config(self, input_info: InputInfo, use_cudagraph: bool) -> SplitConfig:
+        return self._splitter(self, input_info, use_cudagraph)  # type: ignore[arg-type]
+
+    def before_execute(self, batch_idx: int, op: OperatorHandle) -> None:
+        """Hook for hosts; does nothing by default."""
+
+    async def schedule(self, context: ExecutionContext) -> None:
+        n = context.split_config.num_nano_batches
+        if n == 1:
+            self.before_execute(0, None)  # type: ignore[arg-type]
+            while (op := await context.pop(0)) is not None:
+                await context.execute((op,), self._func_for(op))
+            return
+        ordered = {kind for kind, _ in self.SEQUENCE}
+        live = list(range(n))
+        turn_of = list(self.WARM_UP)          # whose turn it is, and for which kind of operator
+        position = -len(self.WARM_UP)
+        current = live[0]
+        held: list[OperatorHandle | None] = [None] * n
+        while live:
+            if held[current] is not None:
+                op, held[current] = held[current], None
+            else:
+                op = await context.pop(current)
+                if op is None:                 # this nano-batch is done: the other one takes the next turn
+                    live.remove(current)
+                    current ^= 1
+                    position += 1
+                    continue
+                if not ordered.intersection(op.tag):
+                    with _on(self.comp_stream):
+                        await context.execute((op,), self._func_for(op))
+                    continue
+                if turn_of[position][1] != current:
+                    held[current] = op          # too early: hold it, let the other nano-batch catch up
+                    current ^= 1
+                    continue
+            assert turn_of[position][0] in op.tag, f"expected a {turn_of[position][0]} operator, got {op.tag}"
+            position += 1
+            if position > 0:
+                position %= len(self.SEQUENCE)
+            elif position == 0:
+                turn_of = list(self.SEQUENCE)
+            self.before_execute(current, op)
+            await self._run(context, op)

@@ -123,3 +123,72 @@ def skewed_trace(ops_per_batch: list[list[str]]) -> list[tuple[str, int]]:
             trace.append((ops_per_batch[b][cursors[b]], b))
             cursors[b] += 1
     return trace
+
+
+DBO_WARM_UP = [("attention", 0)]
+DBO_SEQUENCE = [("attention", 1), ("dispatch", 0), ("expert", 0), ("dispatch", 1), ("expert", 1), ("combine", 0),
+                ("attention", 0), ("combine", 1)]
+
+
+def dbo_trace(ops_per_batch: list[list[tuple[str, list[str]]]]) -> list[tuple[str, int, str]]:
+    """Dispatch order of the dual-batch-overlap policy for MoE layers
+    (``examples/ae/scheduler/vllm/dbo.py:154-220``). ``ops_per_batch[b]`` is the program-order
+    list of ``(subgraph name, tags)`` of nano-batch ``b``. Returns ``(name, batch, stream)`` with
+    stream ``"comm"`` for ``network``-tagged operators and ``"comp"`` otherwise (``"default"``,
+    i.e. whatever stream is current, on the one-nano-batch path).
+
+    One nano-batch: program order on the compute stream. Two: after nano-batch 0's first
+    attention, the operators tagged attention / dispatch / expert / combine are executed in the
+    fixed cyclic order attn1, disp0, exp0, disp1, exp1, comb0, attn0, comb1; an operator that
+    arrives before its turn is held back (one per nano-batch) while the other nano-batch
+    proceeds; operators without one of those tags run at once. A finished nano-batch advances
+    the cycle by one position."""
+    n = len(ops_per_batch)
+    cursors = [0] * n
+    trace: list[tuple[str, int, str]] = []
+
+    def pop(b):
+        if cursors[b] >= len(ops_per_batch[b]):
+            return None
+        op = ops_per_batch[b][cursors[b]]
+        cursors[b] += 1
+        return op
+
+    def run(op, b):
+        name, tags = op
+        trace.append((name, b, "comm" if "network" in tags else "comp"))
+
+    if n == 1:
+        while (op := pop(0)) is not None:
+            trace.append((op[0], 0, "default"))   # the single-batch path keeps the current stream
+        return trace
+    keys = {k for k, _ in DBO_SEQUENCE}
+    live = list(range(n))
+    cur, seq, idx = live[0], DBO_WARM_UP, -len(DBO_WARM_UP)
+    held: list = [None] * n
+    while live:
+        assert cur in live
+        if held[cur] is None:
+            op = pop(cur)
+            if op is None:
+                live.remove(cur)
+                cur ^= 1
+                idx += 1
+                continue
+            if not keys.intersection(op[1]):
+                trace.append((op[0], cur, "comp"))
+                continue
+            if seq[idx][1] != cur:
+                held[cur] = op
+                cur ^= 1
+                continue
+        else:
+            op, held[cur] = held[cur], None
+        assert seq[idx][0] in op[1], (seq[idx], op)
+        idx += 1
+        if idx > 0:
+            idx %= len(DBO_SEQUENCE)
+        elif idx == 0:
+            seq = DBO_SEQUENCE
+        run(op, cur)
+    return trace

@@ -13,6 +13,7 @@ the reference is modified. Outputs:
     split_configs.json   get_split_config of the reference NanoFlow policies
     c1_llama.json        partition, tags, dispatch order and sampled logits of the
                          2-layer decoder split into two nano-batches
+    dbo_trace.json       execution order and streams of the reference's DBO (MoE) policy
     mlp_split.npz/.json  bf16 gated-MLP graph executed by the reference in two
                          ragged nano-batches (inputs, weights, output)
 """
@@ -170,6 +171,101 @@ def run_reference(model, inputs, split, pattern, tag, ref):
     return out, trace, tags
 
 
+def golden_dbo_trace(ref_iface, ref_cfg) -> dict:
+    """Runs the reference's DBO policy (``examples/ae/scheduler/vllm/dbo.py``, unmodified) against a
+    scripted engine that hands out tagged operators in program order, and records the order and
+    stream in which the policy executes them. The vLLM names the file imports are provided as
+    empty stand-ins (vLLM's forward context only carries per-nano-batch attention metadata)."""
+    import asyncio
+    import types
+
+    current = {"stream": "default"}
+
+    class _NamedStream:
+        def __init__(self, *a, **k):
+            self.name = None
+
+    class _StreamCtx:
+        def __init__(self, s):
+            self.s = s
+
+        def __enter__(self):
+            self.prev = current["stream"]
+            current["stream"] = self.s.name
+
+        def __exit__(self, *a):
+            current["stream"] = self.prev
+
+    torch.cuda.Stream = _NamedStream  # type: ignore[misc]
+    torch.cuda.stream = lambda s: _StreamCtx(s)  # type: ignore[assignment]
+
+    fwd = types.ModuleType("vllm.forward_context")
+    fwd.DPMetadata = type("DPMetadata", (), {})
+    forward_ctx = types.SimpleNamespace(attn_metadata=["meta0", "meta1"], dp_metadata=None)
+    fwd.get_forward_context = lambda: forward_ctx
+    ln = types.ModuleType("vllm.model_executor.layers.layernorm")
+    ln.RMSNorm = type("RMSNorm", (torch.nn.Module,), {})
+    ds = types.ModuleType("vllm.model_executor.models.deepseek_v2")
+    ds.DeepseekV2MoE = type("DeepseekV2MoE", (torch.nn.Module,), {})
+    for name, mod in (("vllm", types.ModuleType("vllm")), ("vllm.forward_context", fwd),
+                      ("vllm.model_executor", types.ModuleType("vllm.model_executor")),
+                      ("vllm.model_executor.layers", types.ModuleType("vllm.model_executor.layers")),
+                      ("vllm.model_executor.layers.layernorm", ln),
+                      ("vllm.model_executor.models", types.ModuleType("vllm.model_executor.models")),
+                      ("vllm.model_executor.models.deepseek_v2", ds)):
+        sys.modules[name] = mod
+    dbo = load_policy_module(os.path.join(REFERENCE, "examples/ae/scheduler/vllm/dbo.py"), "_ref_dbo")
+    cfg = ref_cfg.DynaFlowConfig("x:y", 2, ref_cfg.InductorConfig(False), ref_cfg.CUDAGraphConfig(False, [64]),
+                                 {"min_nano_split_tokens": 1})
+    policy = dbo.DBOScheduler(cfg)
+    policy.comm_stream.name, policy.comp_stream.name = "comm", "comp"
+
+    def layer(i):
+        return [(f"pre{i}", []), (f"attn{i}", ["attention", "no-cudagraph"]),
+                (f"disp{i}", ["network", "no-inductor", "dispatch"]), (f"exp{i}", ["no-inductor", "expert"]),
+                (f"comb{i}", ["network", "no-inductor", "combine"])]
+
+    cases = []
+    for layers, batches in ((1, 2), (3, 2), (2, 1)):
+        program = sum((layer(i) for i in range(layers)), []) + [("final", [])]
+        trace: list = []
+        forward_ctx.attn_metadata = ["meta0", "meta1"]   # the policy overwrites it with one entry per operator
+
+        async def drive():
+            op_queue = {b: asyncio.Queue(maxsize=10) for b in range(batches)}
+            execute_queue: asyncio.Queue = asyncio.Queue()
+            split = ref_iface.SplitConfig(batches, [1] * batches, list(range(batches + 1)), [1] * batches,
+                                          [1] * batches, list(range(batches + 1)), False, False)
+            context = ref_iface.ExecutionContext(split, op_queue, execute_queue)
+            cursor = [0] * batches
+
+            async def push(b):
+                if cursor[b] < len(program):
+                    name, tags = program[cursor[b]]
+                    cursor[b] += 1
+                    await op_queue[b].put(ref_iface.OperatorHandle(name, b, 1, set(tags), False, False))
+                else:
+                    await op_queue[b].put(None)
+
+            async def engine():
+                for b in range(batches):
+                    await push(b)
+                remaining = batches * len(program)
+                while remaining:
+                    ops, _func, done = await execute_queue.get()
+                    op = ops[0]
+                    trace.append([op.module_name, op.batch_idx, current["stream"]])
+                    remaining -= 1
+                    await push(op.batch_idx)
+                    done.set()
+
+            await asyncio.gather(engine(), policy.schedule(context))
+
+        asyncio.run(drive())
+        cases.append({"layers": layers, "batches": batches, "program": program, "trace": trace})
+    return {"cases": cases}
+
+
 def main() -> None:
     install_cpu_shims()
     sys.path.insert(0, REFERENCE)
@@ -235,6 +331,8 @@ def main() -> None:
                         w_up=bits(mlp.up_proj.weight), w_down=bits(mlp.down_proj.weight), out=bits(out.clone()))
     with open(os.path.join(HERE, "mlp_split.json"), "w") as f:
         json.dump({"split": split, "trace": trace, "tags": tags, "dtype": "bfloat16 as int16 bits"}, f, indent=1)
+    with open(os.path.join(HERE, "dbo_trace.json"), "w") as f:
+        json.dump(golden_dbo_trace(ref_iface, ref_cfg), f, indent=1)
     print("golden fixtures written to", HERE)
 
 

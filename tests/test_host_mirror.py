@@ -265,3 +265,50 @@ def test_c1_llama_against_reference_golden():
             assert run["equal_to_unsplit"] and torch.equal(got, unsplit)  # as observed for the reference
         sample = got[:, ::32, ::1000]
         assert (sample - sample_ref).abs().max() / golden["logits_abs_max"] <= 1e-5
+
+
+def test_dbo_policy_matches_reference_golden(monkeypatch):
+    """The MoE dual-batch-overlap policy against the order and streams the reference's own
+    policy produced for the same tagged operator programs."""
+    import asyncio
+    import contextlib
+
+    import dynaflow_b200.policies as policies
+    from dynaflow_b200.interface import OperatorHandle
+
+    current = {"stream": "default"}
+
+    @contextlib.contextmanager
+    def fake_on(stream):
+        prev, current["stream"] = current["stream"], stream
+        try:
+            yield
+        finally:
+            current["stream"] = prev
+
+    monkeypatch.setattr(policies, "_on", fake_on)
+    for case in _load("dbo_trace.json")["cases"]:
+        program, n = case["program"], case["batches"]
+        policy = policies.DBOScheduler(make_config())
+        policy.comm_stream, policy.comp_stream = "comm", "comp"
+        swaps = []
+        policy.before_execute = lambda b, op: swaps.append(b)
+        trace = []
+
+        class Ctx:
+            split_config = SplitConfig(n, [1] * n, list(range(n + 1)), [1] * n, [1] * n, list(range(n + 1)), False, False)
+            cursor = [0] * n
+
+            async def pop(self, b):
+                if self.cursor[b] >= len(program):
+                    return None
+                name, tags = program[self.cursor[b]]
+                self.cursor[b] += 1
+                return OperatorHandle(name, b, 1, set(tags), False, False)
+
+            async def execute(self, ops, func=None):
+                trace.append([ops[0].module_name, ops[0].batch_idx, current["stream"]])
+
+        asyncio.run(policy.schedule(Ctx()))
+        assert trace == case["trace"], (case["layers"], n)
+        assert swaps, "the per-operator host hook was never called"

@@ -104,3 +104,10 @@ def test_top2_route_and_moe_layer():
     t = 7
     manual = sum(w[t, s] * ops_oracle.gated_mlp(x[t:t + 1], wg[ids[t, s]], wu[ids[t, s]], wd[ids[t, s]]) for s in range(2))
     assert torch.allclose(y[t], manual[0], atol=1e-5)
+
+
+def test_dbo_trace_matches_reference_policy():
+    for case in _load("dbo_trace.json")["cases"]:
+        program = [(n, t) for n, t in case["program"]]
+        got = split_oracle.dbo_trace([program] * case["batches"])
+        assert [list(x) for x in got] == case["trace"], (case["layers"], case["batches"])
