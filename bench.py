@@ -247,13 +247,13 @@ def run_ours(args) -> None:
         def timed(**kw):
             for _ in range(2):
                 residual.zero_()
-                layer.forward_chain(x_dev, cuts, chain_layers, norm_w, residual, fused_norm=args.fused_norm, **kw)
+                layer.forward_chain(x_dev, cuts, chain_layers, norm_w, residual, fused_norm=args.fused_norm, sharded_residual=not args.replicated_residual, **kw)
             barrier()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             reps = max(4, args.steps // 16)
             a.record()
             for _ in range(reps):
-                layer.forward_chain(x_dev, cuts, chain_layers, norm_w, residual, fused_norm=args.fused_norm, **kw)
+                layer.forward_chain(x_dev, cuts, chain_layers, norm_w, residual, fused_norm=args.fused_norm, sharded_residual=not args.replicated_residual, **kw)
             b.record()
             barrier()
             return max_over_ranks(a.elapsed_time(b) / reps / chain_layers)
@@ -264,8 +264,11 @@ def run_ours(args) -> None:
         payload = ROWS * H * 2  # bytes reduced per block (all micro-batches)
         wire = 2.0 * (world - 1) / world * payload
         peak_tf = float(measured_peaks()[0]["bf16_tflops"])
-        comm_stats = {"chain": f"{chain_layers} TP MLP blocks back to back; between them all-reduce + residual + RMSNorm "
-                               + ("in one launch" if args.fused_norm else "(reduction on few CTAs, normalisation over all SMs)"),
+        comm_stats = {"chain": f"{chain_layers} TP MLP blocks back to back; between them all-reduce + residual + RMSNorm: "
+                               + ("reduce-scatter, add + norm on the owned rows (residual sharded by rows), all-gather, one launch"
+                                  if not args.replicated_residual else
+                                  ("replicated residual, one launch" if args.fused_norm
+                                   else "replicated residual, reduction on few CTAs then normalisation over all SMs")),
                       "ms_per_block_overlapped": t_overlap, "ms_per_block_compute_only": t_compute,
                       "ms_per_block_comm_only": t_comm,
                       "hidden_frac": 1.0 - (t_overlap - t_compute) / t_comm,
@@ -415,6 +418,8 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=ROWS, help="rows per step (default: the benchmark's 16384; "
                     "smaller values are for profiler captures only)")
     ap.add_argument("--comm-ctas", type=int, default=32, help="CTAs of the peer-memory all-reduce kernel (N > 1)")
+    ap.add_argument("--replicated-residual", action="store_true",
+                    help="N > 1 chain: keep the residual stream replicated on every rank instead of sharded by rows")
     ap.add_argument("--fused-norm", action="store_true", help="N > 1 chain: one-launch all-reduce+RMSNorm kernel")
     ap.add_argument("--no-sweep", action="store_true", help="skip the M sweep (profiling runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")

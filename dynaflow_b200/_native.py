@@ -59,6 +59,7 @@ SIGNATURES: dict[str, tuple] = {
     "df_comm_region_free": (_i, [_vp]),
     "df_allreduce_bf16": (_i, [_rank_p, _i, _i, _i, _i, _i, _vp, _vp]),
     "df_allreduce_add_rmsnorm_bf16": (_i, [_rank_p, _i, _i, _i, _i, _vp, _f, _i, _vp, _vp]),
+    "df_allreduce_add_rmsnorm_sharded_bf16": (_i, [_rank_p, _i, _i, _i, _i, _vp, _f, _i, _vp, _vp]),
     "df_add_rmsnorm_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _i, _i, _vp]),
     "df_allreduce_emulated_bf16": (_i, [_rank_p, _i, _i, _i, _i, _vp, _f, _i, _i, _vp, _vp]),
     "df_mlp_gated_bf16_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),

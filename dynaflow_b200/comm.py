@@ -157,6 +157,26 @@ class PeerComm(_Regions):
         self.bytes_reduced += rows * self.hidden * 2
         return out
 
+    def all_reduce_add_rmsnorm_sharded(self, slot: int, rows: int, residual: torch.Tensor, weight: torch.Tensor,
+                                       eps: float = 1e-5, first: bool = False) -> torch.Tensor:
+        """Reduce-scatter, residual add + RMSNorm on this rank's row slice, all-gather. ``residual``
+        is ``[rows, hidden]`` on every rank but only the rows ``slice_bounds(rows)`` are read and
+        updated here (the residual stream is sharded by rows); ``first=True`` treats it as zeros.
+        Returns the normalised rows of all ranks (``result(slot, rows)``)."""
+        view = self._view(self.rank, self.regions[slot], None if first else residual, residual, None)
+        rc = self.lib.df_allreduce_add_rmsnorm_sharded_bf16(ctypes.byref(view), self.world, self.max_rows, self.hidden,
+                                                            rows, weight.data_ptr(), eps, self.n_ctas, self._status_ptr,
+                                                            torch.cuda.current_stream(self.device).cuda_stream)
+        if rc != 0:
+            _check(rc, "df_allreduce_add_rmsnorm_sharded_bf16")
+        self.launches += 1
+        self.bytes_reduced += rows * self.hidden * 2
+        return self._sums[slot][:rows]
+
+    def slice_bounds(self, rows: int) -> tuple[int, int]:
+        """Rows of a ``rows``-row message that this rank owns."""
+        return rows * self.rank // self.world, rows * (self.rank + 1) // self.world
+
     def summary(self) -> dict:
         return {"kind": "peer-memory two-shot all-reduce (hand-written, no NCCL on the data path)",
                 "n_ctas": self.n_ctas, "launches": self.launches, "payload_bytes": self.bytes_reduced}
@@ -204,16 +224,18 @@ class EmulatedComm(_Regions):
         return b.view(torch.bfloat16).view(self.max_rows, self.hidden)[:rows]
 
     def run(self, rows: int, *, weight: torch.Tensor | None = None, residual_in: list | None = None,
-            residual_out: list | None = None, out: list | None = None, eps: float = 1e-5) -> None:
+            residual_out: list | None = None, out: list | None = None, eps: float = 1e-5,
+            sharded: bool = False) -> None:
         fuse = weight is not None
         views = (df_comm_rank_t * self.world)()
         for r in range(self.world):
             v = self._view(r, self.ptrs, residual_in[r] if (fuse and residual_in) else None,
-                           residual_out[r] if fuse else None, out[r] if fuse else None)
+                           residual_out[r] if fuse else None, out[r] if (fuse and not sharded) else None)
             views[r] = v
         st = ops.status_block(self.device)
         _check(self.lib.df_allreduce_emulated_bf16(views, self.world, self.max_rows, self.hidden, rows,
-                                                   weight.data_ptr() if fuse else None, eps, 1 if fuse else 0,
+                                                   weight.data_ptr() if fuse else None, eps,
+                                                   (2 if sharded else 1) if fuse else 0,
                                                    self.n_ctas, st.data_ptr(),
                                                    torch.cuda.current_stream(self.device).cuda_stream),
                "df_allreduce_emulated_bf16")

@@ -17,6 +17,11 @@
 //               this rank -- nothing (the result is the sum buffer), or
 //               r' = y + residual; out = rmsnorm(r') * w
 //
+// Third form ("sharded residual"): the residual stream is kept sharded by rows, rank r holding
+// the rows of slice r. The owner then does r' = y + residual and the RMSNorm BETWEEN the two
+// shots, on its own rows only, and the second shot distributes the normalised rows; there is
+// no phase 2, no replicated work and no traffic beyond that of the plain all-reduce.
+//
 // Blocks only ever synchronise with the same-index block of the other ranks,
 // and block b consumes in phase 2 exactly the rows that the blocks b produced,
 // so there is no grid-wide barrier. Flags carry a per-block sequence number
@@ -60,7 +65,7 @@ constexpr size_t kHeaderBytes = 8192;
 
 static size_t align256(size_t x) { return (x + 255) / 256 * 256; }
 
-enum : int { EPI_NONE = 0, EPI_ADD_RMSNORM = 1 };
+enum : int { EPI_NONE = 0, EPI_ADD_RMSNORM = 1, EPI_ADD_RMSNORM_SHARDED = 2 };
 
 struct RankView {
   int rank;
@@ -230,7 +235,7 @@ __global__ void __launch_bounds__(kCommThreads, 2) allreduce_kernel(const CommPa
   extern __shared__ uint4 s_weight[];
   const RankView& me = p.ranks[EMULATE ? blockIdx.y : 0];
   if (threadIdx.x == 0) s_abort = 0u;
-  if (EPI == EPI_ADD_RMSNORM && p.H <= kMaxSmemHidden) {
+  if (EPI != EPI_NONE && p.H <= kMaxSmemHidden) {
     for (int v = threadIdx.x; v < (p.H >> 3); v += blockDim.x) s_weight[v] = reinterpret_cast<const uint4*>(p.weight)[v];
   }
   const unsigned long long t_end = globaltimer_ns() + p.timeout_ns;
@@ -250,16 +255,22 @@ __global__ void __launch_bounds__(kCommThreads, 2) allreduce_kernel(const CommPa
     // so the bytes in flight (CTAs x 8 warps x 32 lanes x U x 16 B per peer), not the issue
     // rate, set the bandwidth. U x W = 16 loads per lane keeps the register count level.
     constexpr int U = (W <= 2) ? 8 : (W <= 4 ? 4 : 2);
+    const uint4* wv1 = (p.H <= kMaxSmemHidden) ? s_weight : reinterpret_cast<const uint4*>(p.weight);
     for (int row = lo + row_first; row < hi; row += row_stride) {
       const size_t base = static_cast<size_t>(row) * p.H;
+      float ss = 0.0f;
       for (int v0 = lane; v0 < nvec; v0 += 32 * U) {
         uint4 in[U][W];
+        uint4 rs[(EPI == EPI_ADD_RMSNORM_SHARDED) ? U : 1];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           const int v = v0 + 32 * u;
           if (v < nvec) {
 #pragma unroll
             for (int r = 0; r < W; ++r) in[u][r] = __ldcg(reinterpret_cast<const uint4*>(me.partial[r] + base) + v);
+            if (EPI == EPI_ADD_RMSNORM_SHARDED)  // issued together with the peer loads, not behind them
+              rs[u] = me.residual_in != nullptr ? reinterpret_cast<const uint4*>(me.residual_in + base)[v]
+                                                : make_uint4(0u, 0u, 0u, 0u);
           }
         }
 #pragma unroll
@@ -274,8 +285,52 @@ __global__ void __launch_bounds__(kCommThreads, 2) allreduce_kernel(const CommPa
               for (int i = 0; i < 8; ++i) acc[i] += f[i];
             }
             const uint4 y = pack8(acc);
+            if (EPI == EPI_ADD_RMSNORM_SHARDED) {
+              // the owner of the row adds its residual rows here, between the two shots: the
+              // new residual stays on this rank only (the residual stream is sharded by rows)
+              float fy[8], fr[8];
+              unpack8(y, fy);
+              unpack8(rs[(EPI == EPI_ADD_RMSNORM_SHARDED) ? u : 0], fr);
 #pragma unroll
-            for (int r = 0; r < W; ++r) __stcg(reinterpret_cast<uint4*>(me.sum[r] + base) + v, y);
+              for (int i = 0; i < 8; ++i) fy[i] += fr[i];
+              const uint4 packed = pack8(fy);
+              reinterpret_cast<uint4*>(me.residual_out + base)[v] = packed;
+              unpack8(packed, fy);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) ss += fy[i] * fy[i];
+            } else {
+#pragma unroll
+              for (int r = 0; r < W; ++r) __stcg(reinterpret_cast<uint4*>(me.sum[r] + base) + v, y);
+            }
+          }
+        }
+      }
+      if (EPI == EPI_ADD_RMSNORM_SHARDED) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        const float inv = rsqrtf(ss / static_cast<float>(p.H) + p.eps);
+        const uint4* rnew = reinterpret_cast<const uint4*>(me.residual_out + base);
+        constexpr int kBatch = 8;
+        for (int v0 = lane; v0 < nvec; v0 += 32 * kBatch) {
+          uint4 xv[kBatch];
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u) {
+            const int v = v0 + 32 * u;
+            if (v < nvec) xv[u] = rnew[v];  // this thread's own writes
+          }
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u) {
+            const int v = v0 + 32 * u;
+            if (v < nvec) {
+              float fx[8], fw[8];
+              unpack8(xv[u], fx);
+              unpack8(wv1[v], fw);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) fx[i] = __bfloat162float(__float2bfloat16_rn(fx[i] * inv)) * fw[i];
+              const uint4 outv = pack8(fx);
+#pragma unroll
+              for (int r = 0; r < W; ++r) __stcg(reinterpret_cast<uint4*>(me.sum[r] + base) + v, outv);
+            }
           }
         }
       }
@@ -325,7 +380,9 @@ static int launch_allreduce(const CommParams& p, int n_ctas, int emulated, void*
   case W:                                                                                        \
     fn = (p.mode == EPI_ADD_RMSNORM)                                                             \
              ? reinterpret_cast<const void*>(&allreduce_kernel<W, EMULATE, EPI_ADD_RMSNORM>)     \
-             : reinterpret_cast<const void*>(&allreduce_kernel<W, EMULATE, EPI_NONE>);           \
+             : (p.mode == EPI_ADD_RMSNORM_SHARDED)                                               \
+                   ? reinterpret_cast<const void*>(&allreduce_kernel<W, EMULATE, EPI_ADD_RMSNORM_SHARDED>) \
+                   : reinterpret_cast<const void*>(&allreduce_kernel<W, EMULATE, EPI_NONE>);     \
     break;
     DF_CASE(1) DF_CASE(2) DF_CASE(3) DF_CASE(4) DF_CASE(5) DF_CASE(6) DF_CASE(7) DF_CASE(8)
 #undef DF_CASE
@@ -333,7 +390,7 @@ static int launch_allreduce(const CommParams& p, int n_ctas, int emulated, void*
       return fail(DF_EUNSUPPORTED, "world size %d is outside [1, %d]", p.world, kMaxWorld);
   }
   cudaError_t e;
-  const size_t smem = (p.mode == EPI_ADD_RMSNORM && p.H <= kMaxSmemHidden) ? static_cast<size_t>(p.H) * 2 : 0;
+  const size_t smem = (p.mode != EPI_NONE && p.H <= kMaxSmemHidden) ? static_cast<size_t>(p.H) * 2 : 0;
   if (EMULATE) {
     // every emulated rank must be resident at once: its blocks wait on the others'
     e = cudaLaunchCooperativeKernel(fn, grid, block, args, smem, static_cast<cudaStream_t>(stream));
@@ -354,7 +411,7 @@ static int fill_params(CommParams* p, int n_views, const df_comm_rank_t* views, 
   if (T <= 0 || H <= 0 || (H % 8) != 0) return fail(DF_EINVAL, "T must be positive and H a positive multiple of 8");
   if (H != hidden || T > max_rows)
     return fail(DF_EINVAL, "T=%d, H=%d do not fit the region (max_rows=%d, hidden=%d)", T, H, max_rows, hidden);
-  if (mode == EPI_ADD_RMSNORM && weight == nullptr) return fail(DF_EINVAL, "RMSNorm weight is NULL");
+  if (mode != EPI_NONE && weight == nullptr) return fail(DF_EINVAL, "RMSNorm weight is NULL");
   const RegionLayout l = region_layout(max_rows, hidden);
   std::memset(p, 0, sizeof(*p));
   for (int v = 0; v < n_views; ++v) {
@@ -374,6 +431,12 @@ static int fill_params(CommParams* p, int n_views, const df_comm_rank_t* views, 
     out.residual_in = static_cast<const __nv_bfloat16*>(in.residual_in);
     out.residual_out = static_cast<__nv_bfloat16*>(in.residual_out);
     out.out = static_cast<__nv_bfloat16*>(in.out);
+    if (mode == EPI_ADD_RMSNORM_SHARDED) {
+      if (in.residual_out == nullptr) return fail(DF_EINVAL, "residual_out is NULL");
+      if ((reinterpret_cast<uintptr_t>(in.residual_out) & 15u) || (reinterpret_cast<uintptr_t>(in.residual_in) & 15u) ||
+          (reinterpret_cast<uintptr_t>(weight) & 15u))
+        return fail(DF_EINVAL, "residual and weight pointers must be 16-byte aligned");
+    }
     if (mode == EPI_ADD_RMSNORM) {
       if (in.residual_out == nullptr || in.out == nullptr) return fail(DF_EINVAL, "residual_out / out is NULL");
       if ((reinterpret_cast<uintptr_t>(in.residual_out) & 15u) || (reinterpret_cast<uintptr_t>(in.out) & 15u) ||
@@ -477,6 +540,16 @@ int df_allreduce_add_rmsnorm_bf16(const df_comm_rank_t* view, int world, int max
   return df::launch_allreduce<false>(p, df::clamp_ctas(n_ctas), 1, stream);
 }
 
+int df_allreduce_add_rmsnorm_sharded_bf16(const df_comm_rank_t* view, int world, int max_rows, int hidden, int T,
+                                          const void* weight, float eps, int n_ctas, df_status_t* dev_status,
+                                          void* stream) {
+  df::CommParams p;
+  int r = df::fill_params(&p, 1, view, world, max_rows, hidden, T, hidden, df::EPI_ADD_RMSNORM_SHARDED, weight, eps,
+                          dev_status);
+  if (r != DF_OK) return r;
+  return df::launch_allreduce<false>(p, df::clamp_ctas(n_ctas), 1, stream);
+}
+
 int df_add_rmsnorm_bf16(const void* y, const void* residual_in, void* residual_out, void* out, const void* weight,
                         float eps, int T, int H, void* stream) {
   if (y == nullptr || residual_out == nullptr || out == nullptr || weight == nullptr)
@@ -504,8 +577,8 @@ int df_allreduce_emulated_bf16(const df_comm_rank_t* views, int world, int max_r
                                const void* weight, float eps, int fuse_rmsnorm, int n_ctas, df_status_t* dev_status,
                                void* stream) {
   df::CommParams p;
-  int r = df::fill_params(&p, world, views, world, max_rows, hidden, T, hidden,
-                          fuse_rmsnorm ? df::EPI_ADD_RMSNORM : df::EPI_NONE, weight, eps, dev_status);
+  const int mode = fuse_rmsnorm == 2 ? df::EPI_ADD_RMSNORM_SHARDED : (fuse_rmsnorm ? df::EPI_ADD_RMSNORM : df::EPI_NONE);
+  int r = df::fill_params(&p, world, views, world, max_rows, hidden, T, hidden, mode, weight, eps, dev_status);
   if (r != DF_OK) return r;
   for (int v = 0; v < world; ++v)
     if (views[v].rank != v) return df::fail(DF_EINVAL, "emulated views must be listed in rank order");

@@ -119,13 +119,17 @@ class TensorParallelGatedMLP:
 
     def forward_chain(self, x: torch.Tensor, cuts: list[int], layers: int, norm_weight: torch.Tensor,
                       residual: torch.Tensor, skip_comm: bool = False, skip_compute: bool = False,
-                      fused_norm: bool = True) -> list[torch.Tensor]:
+                      fused_norm: bool = True, sharded_residual: bool = False) -> list[torch.Tensor]:
         """``layers`` tensor-parallel MLP blocks back to back, the way a decoder runs them: for
         every micro-batch ``x <- rmsnorm(allreduce(mlp(x)) + residual) * w`` with the fused
         reduction kernel on the communication stream, so that the reduction of micro-batch
         ``i`` runs under the GEMMs of micro-batch ``i+1`` -- of the same block or, for the last
         micro-batch, of the next block. (All blocks share this object's weights; it exists to
-        measure the steady-state overlap.) Returns the per-micro-batch outputs."""
+        measure the steady-state overlap.) With ``sharded_residual`` the residual stream is
+        sharded by rows and the add + RMSNorm happen inside the reduction, between its two
+        shots; the block's output is then the communicator's result buffer, which the next
+        block's reduction of the same micro-batch overwrites -- after that block's GEMMs have
+        consumed it. Returns the per-micro-batch outputs."""
         assert self.world > 1 and self.comm is not None
         main = torch.cuda.current_stream(self.device)
         comm_stream = self.comm.stream
@@ -150,12 +154,18 @@ class TensorParallelGatedMLP:
                 if not skip_comm:
                     comm_stream.wait_event(ready)
                     with torch.cuda.stream(comm_stream):
-                        self.comm.all_reduce_add_rmsnorm(slot, rows, res[mb], norm_weight, outs[mb], res[mb],
-                                                         fused=fused_norm)
+                        if sharded_residual:
+                            nxt = self.comm.all_reduce_add_rmsnorm_sharded(slot, rows, res[mb], norm_weight)
+                        else:
+                            self.comm.all_reduce_add_rmsnorm(slot, rows, res[mb], norm_weight, outs[mb], res[mb],
+                                                             fused=fused_norm)
+                            nxt = outs[mb]
                         done = torch.cuda.Event()
                         done.record(comm_stream)
                     reduced[mb] = done
-                    xs[mb] = outs[mb]
+                    xs[mb] = nxt
+                    if sharded_residual:
+                        outs[mb] = nxt
         main.wait_stream(comm_stream)
         return outs
 

@@ -185,6 +185,17 @@ int df_allreduce_add_rmsnorm_bf16(const df_comm_rank_t* view, int world, int max
                                   const void* weight, float eps, int n_ctas, df_status_t* dev_status,
                                   void* stream);
 
+/* The same with the residual stream SHARDED BY ROWS (what a tensor-parallel decoder needs, since
+ * the residual is only ever added to the next reduction's output): rank r reads and updates
+ * view->residual_in / residual_out for the rows [T*r/world, T*(r+1)/world) only, does the add
+ * and the RMSNorm on those rows between the reduce-scatter and the all-gather, and the
+ * normalised rows of all ranks land in every rank's `sum` buffer. Same per-row arithmetic as
+ * the call above; no work is replicated and no extra bytes move. view->out is unused.
+ * (tokenweave.cu:38-113 has this structure with in-switch reduction; here over peer memory.) */
+int df_allreduce_add_rmsnorm_sharded_bf16(const df_comm_rank_t* view, int world, int max_rows, int hidden, int T,
+                                          const void* weight, float eps, int n_ctas, df_status_t* dev_status,
+                                          void* stream);
+
 /* The second half of the fused call as its own launch over all SMs:
  * r' = y + residual_in (NULL = zeros); out = bf16(r' * rsqrt(mean(r'^2) + eps)) * weight;
  * residual_out = r' (may equal residual_in). The RMSNorm(+residual) module a host model
@@ -199,8 +210,8 @@ int df_add_rmsnorm_bf16(const void* y, const void* residual_in, void* residual_o
  * memory. Exercises the flag protocol and the arithmetic without a second GPU.
  * No counterpart in the reference. */
 int df_allreduce_emulated_bf16(const df_comm_rank_t* views, int world, int max_rows, int hidden, int T,
-                               const void* weight, float eps, int fuse_rmsnorm, int n_ctas,
-                               df_status_t* dev_status, void* stream);
+                               const void* weight, float eps, int fuse_rmsnorm /* 0 none, 1 replicated, 2 sharded residual */,
+                               int n_ctas, df_status_t* dev_status, void* stream);
 
 /* Size of the library-owned scratch behind df_mlp_gated_bf16_static: 64 MiB of
  * static device memory, held by every GPU that loads the library until the

@@ -96,6 +96,21 @@ def main() -> None:
     rel = ((res_dev.cpu().float() - ro.float()).abs().max() / ro.float().abs().max()).item()
     assert rel <= 2e-2, f"rank {rank}: chained residual rel err {rel}"
     dist.barrier()
+
+    # ---- the same chain with the residual stream sharded by rows (add + norm between the two shots)
+    res_dev = res0.to(dev)
+    outs = layer.forward_chain(x.to(dev), [0, T, 2 * T], 2, norm_w.to(dev), res_dev, sharded_residual=True)
+    torch.cuda.synchronize()
+    ops.check_status()
+    got = torch.cat([o.cpu() for o in outs])
+    rel = ((got.float() - xo.float()).abs().max() / xo.float().abs().max()).item()
+    assert rel <= 2e-2, f"rank {rank}: sharded-residual chain rel err {rel}"
+    for mb in range(2):                                   # this rank's residual rows of each micro-batch
+        lo, hi = comm.slice_bounds(T)
+        mine = res_dev[mb * T + lo: mb * T + hi].cpu().float()
+        ref = ro[mb * T + lo: mb * T + hi].float()
+        assert ((mine - ref).abs().max() / ro.float().abs().max()).item() <= 2e-2, f"rank {rank}: residual slice"
+    dist.barrier()
     comm.close()
     dist.destroy_process_group()
     if rank == 0:

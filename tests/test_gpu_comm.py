@@ -126,3 +126,38 @@ def test_standalone_add_rmsnorm_equals_the_fused_second_half(comm_mod):
     res0 = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
     comm_mod.add_rmsnorm(y.cuda(), None, w.cuda(), out0, res0)   # no residual: r' = y
     assert torch.equal(res0.cpu(), y)
+
+
+@pytest.mark.parametrize("world,T,H", [(2, 48, 256), (8, 203, 4096), (4, 33, 1024), (1, 16, 128)])
+@pytest.mark.parametrize("with_residual", [True, False])
+def test_emulated_sharded_residual_form(comm_mod, world, T, H, with_residual):
+    """Residual stream sharded by rows: the owner of a row slice adds the residual and normalises
+    between the two shots; every rank receives the normalised rows of all slices, and only the
+    owner's residual rows change."""
+    from dynaflow_b200 import ops
+    from oracle import ops_oracle
+
+    g = torch.Generator().manual_seed(13 * world + T)
+    parts = [torch.randn(T, H, generator=g).bfloat16() for _ in range(world)]
+    residual = torch.randn(T, H, generator=g).bfloat16()
+    weight = (1.0 + 0.1 * torch.randn(H, generator=g)).bfloat16()
+    want_out, want_res = ops_oracle.allreduce_add_rmsnorm(parts, residual if with_residual else None, weight)
+    em = comm_mod.EmulatedComm(world, max_rows=256, hidden=H, n_ctas=8)
+    for r in range(world):
+        em.partial(r, T).copy_(parts[r])
+    sentinel = 7.0
+    res_bufs = [(residual.clone() if with_residual else torch.full((T, H), sentinel).bfloat16()).cuda()
+                for _ in range(world)]
+    em.run(T, weight=weight.cuda(), residual_in=res_bufs if with_residual else None, residual_out=res_bufs,
+           sharded=True)
+    torch.cuda.synchronize()
+    ops.check_status()
+    for r in range(world):
+        assert _rel(em.result(r, T), want_out) <= TOL
+        assert torch.equal(em.result(r, T), em.result(0, T))
+        lo, hi = T * r // world, T * (r + 1) // world
+        assert torch.equal(res_bufs[r][lo:hi].cpu(), want_res[lo:hi])            # own slice updated
+        before = residual if with_residual else torch.full((T, H), sentinel).bfloat16()
+        keep = torch.ones(T, dtype=torch.bool)
+        keep[lo:hi] = False
+        assert torch.equal(res_bufs[r].cpu()[keep], before[keep])                # other rows untouched
