@@ -33,6 +33,7 @@ if ROOT not in sys.path:
 H, I = 4096, 14336
 ROWS = 16384
 MICRO_BATCHES = 2
+GATEUP_DRAM_BYTES_PER_LAUNCH = 788_613_632
 METRIC = "prefill tokens/sec through the fused gated-MLP layer (2 micro-batches)"
 
 
@@ -306,11 +307,9 @@ def run_ours(args) -> None:
     achieved = gateup_flops / (gateup_ms * 1e-3) / 1e12
     peak = float(peaks["bf16_tflops"])
     step_flops = 6.0 * ROWS * H * (I // world)
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "gateup_traffic.json")
-    if os.path.exists(tpath):
-        with open(tpath) as f:
-            traffic = json.load(f).get("dram_bytes_per_launch")
+    # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at 8192 rows, from the 1-pass ncu
+    # capture summarised in profiles/gated_mlp_launch_list_rows16384.md; it only describes that shape
+    traffic = GATEUP_DRAM_BYTES_PER_LAUNCH if (ROWS == 16384 and world == 1) else None
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
