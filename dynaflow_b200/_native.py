@@ -58,6 +58,13 @@ SIGNATURES: dict[str, tuple] = {
     "df_comm_region_close": (_i, [_vp]),
     "df_comm_region_free": (_i, [_vp]),
     "df_allreduce_bf16": (_i, [_rank_p, _i, _i, _i, _i, _i, _vp, _vp]),
+    "df_all_gather_bf16": (_i, [_rank_p, _i, _i, _i, _i, _i, _vp, _vp]),
+    "df_reduce_scatter_bf16": (_i, [_rank_p, _i, _i, _i, _i, _i, _vp, _vp]),
+    "df_moe_route_top2": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
+    "df_moe_select_rows": (_i, [_vp, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "df_moe_gather_rows": (_i, [_vp, _vp, _vp, _i, _i, _vp, _vp]),
+    "df_moe_scatter_rows": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp]),
+    "df_mlp_gated_bf16_rows_on_device": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _vp]),
     "df_allreduce_add_rmsnorm_bf16": (_i, [_rank_p, _i, _i, _i, _i, _vp, _f, _i, _vp, _vp]),
     "df_allreduce_add_rmsnorm_sharded_bf16": (_i, [_rank_p, _i, _i, _i, _i, _vp, _f, _i, _vp, _vp]),
     "df_add_rmsnorm_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _i, _i, _vp]),

@@ -82,6 +82,7 @@ struct CommParams {
   RankView ranks[kMaxWorld];   // [0] only, unless several ranks are emulated on one GPU
   const __nv_bfloat16* weight;
   int world, T, H, mode;
+  int coll;  // 0 = all-reduce, 1 = reduce-scatter (keep the reduced slice local), 2 = all-gather of the slices
   float eps;
   unsigned long long timeout_ns;
   Status* status;
@@ -255,6 +256,9 @@ __global__ void __launch_bounds__(kCommThreads, 2) allreduce_kernel(const CommPa
     // so the bytes in flight (CTAs x 8 warps x 32 lanes x U x 16 B per peer), not the issue
     // rate, set the bandwidth. U x W = 16 loads per lane keeps the register count level.
     constexpr int U = (W <= 2) ? 8 : (W <= 4 ? 4 : 2);
+    // reduce-scatter: the reduced rows stay on this rank; all-gather: only this rank's own
+    // partial rows are read (they are the data), and they go to everyone
+    const bool load_all = p.coll != 2, store_all = p.coll != 1;
     const uint4* wv1 = (p.H <= kMaxSmemHidden) ? s_weight : reinterpret_cast<const uint4*>(p.weight);
     for (int row = lo + row_first; row < hi; row += row_stride) {
       const size_t base = static_cast<size_t>(row) * p.H;
@@ -267,7 +271,9 @@ __global__ void __launch_bounds__(kCommThreads, 2) allreduce_kernel(const CommPa
           const int v = v0 + 32 * u;
           if (v < nvec) {
 #pragma unroll
-            for (int r = 0; r < W; ++r) in[u][r] = __ldcg(reinterpret_cast<const uint4*>(me.partial[r] + base) + v);
+            for (int r = 0; r < W; ++r)
+              in[u][r] = (load_all || r == me.rank) ? __ldcg(reinterpret_cast<const uint4*>(me.partial[r] + base) + v)
+                                                    : make_uint4(0u, 0u, 0u, 0u);
             if (EPI == EPI_ADD_RMSNORM_SHARDED)  // issued together with the peer loads, not behind them
               rs[u] = me.residual_in != nullptr ? reinterpret_cast<const uint4*>(me.residual_in + base)[v]
                                                 : make_uint4(0u, 0u, 0u, 0u);
@@ -300,7 +306,8 @@ __global__ void __launch_bounds__(kCommThreads, 2) allreduce_kernel(const CommPa
               for (int i = 0; i < 8; ++i) ss += fy[i] * fy[i];
             } else {
 #pragma unroll
-              for (int r = 0; r < W; ++r) __stcg(reinterpret_cast<uint4*>(me.sum[r] + base) + v, y);
+              for (int r = 0; r < W; ++r)
+                if (store_all || r == me.rank) __stcg(reinterpret_cast<uint4*>(me.sum[r] + base) + v, y);
             }
           }
         }
@@ -405,7 +412,7 @@ static int launch_allreduce(const CommParams& p, int n_ctas, int emulated, void*
 }
 
 static int fill_params(CommParams* p, int n_views, const df_comm_rank_t* views, int world, int max_rows, int hidden,
-                       int T, int H, int mode, const void* weight, float eps, df_status_t* dev_status) {
+                       int T, int H, int mode, const void* weight, float eps, df_status_t* dev_status, int coll = 0) {
   if (views == nullptr || dev_status == nullptr) return fail(DF_EINVAL, "NULL pointer argument");
   if (world < 1 || world > kMaxWorld) return fail(DF_EUNSUPPORTED, "world size %d is outside [1, %d]", world, kMaxWorld);
   if (T <= 0 || H <= 0 || (H % 8) != 0) return fail(DF_EINVAL, "T must be positive and H a positive multiple of 8");
@@ -449,6 +456,7 @@ static int fill_params(CommParams* p, int n_views, const df_comm_rank_t* views, 
   p->T = T;
   p->H = H;
   p->mode = mode;
+  p->coll = coll;
   p->eps = eps;
   p->timeout_ns = timeout_ns();
   p->status = reinterpret_cast<Status*>(dev_status);
@@ -532,6 +540,22 @@ int df_allreduce_bf16(const df_comm_rank_t* view, int world, int max_rows, int h
   return df::launch_allreduce<false>(p, df::clamp_ctas(n_ctas), 1, stream);
 }
 
+int df_reduce_scatter_bf16(const df_comm_rank_t* view, int world, int max_rows, int hidden, int T, int n_ctas,
+                           df_status_t* dev_status, void* stream) {
+  df::CommParams p;
+  int r = df::fill_params(&p, 1, view, world, max_rows, hidden, T, hidden, df::EPI_NONE, nullptr, 0.0f, dev_status, 1);
+  if (r != DF_OK) return r;
+  return df::launch_allreduce<false>(p, df::clamp_ctas(n_ctas), 1, stream);
+}
+
+int df_all_gather_bf16(const df_comm_rank_t* view, int world, int max_rows, int hidden, int T, int n_ctas,
+                       df_status_t* dev_status, void* stream) {
+  df::CommParams p;
+  int r = df::fill_params(&p, 1, view, world, max_rows, hidden, T, hidden, df::EPI_NONE, nullptr, 0.0f, dev_status, 2);
+  if (r != DF_OK) return r;
+  return df::launch_allreduce<false>(p, df::clamp_ctas(n_ctas), 1, stream);
+}
+
 int df_allreduce_add_rmsnorm_bf16(const df_comm_rank_t* view, int world, int max_rows, int hidden, int T,
                                   const void* weight, float eps, int n_ctas, df_status_t* dev_status, void* stream) {
   df::CommParams p;
@@ -577,8 +601,9 @@ int df_allreduce_emulated_bf16(const df_comm_rank_t* views, int world, int max_r
                                const void* weight, float eps, int fuse_rmsnorm, int n_ctas, df_status_t* dev_status,
                                void* stream) {
   df::CommParams p;
-  const int mode = fuse_rmsnorm == 2 ? df::EPI_ADD_RMSNORM_SHARDED : (fuse_rmsnorm ? df::EPI_ADD_RMSNORM : df::EPI_NONE);
-  int r = df::fill_params(&p, world, views, world, max_rows, hidden, T, hidden, mode, weight, eps, dev_status);
+  const int mode = fuse_rmsnorm == 2 ? df::EPI_ADD_RMSNORM_SHARDED : (fuse_rmsnorm == 1 ? df::EPI_ADD_RMSNORM : df::EPI_NONE);
+  const int coll = fuse_rmsnorm == 3 ? 1 : (fuse_rmsnorm == 4 ? 2 : 0);
+  int r = df::fill_params(&p, world, views, world, max_rows, hidden, T, hidden, mode, weight, eps, dev_status, coll);
   if (r != DF_OK) return r;
   for (int v = 0; v < world; ++v)
     if (views[v].rank != v) return df::fail(DF_EINVAL, "emulated views must be listed in rank order");

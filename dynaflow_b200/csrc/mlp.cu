@@ -77,6 +77,9 @@ struct GemmParams {
   // its block index, the next ones come from this counter (zero at launch), so a CTA that
   // shares its SM with the reduction kernel of the other micro-batch simply takes fewer tiles.
   unsigned int* tile_counter;
+  // Row count known only on the device (tokens routed to an expert): if non-NULL, the kernel
+  // processes min(*m_dev, M) rows and M is the capacity the tensor maps were built for.
+  const int* m_dev;
   int debug;  // development only: bit 0 = producer skips the copies, bit 1 = epilogue skips the stores
   unsigned long long timeout_ns;
   __nv_bfloat16* C;
@@ -204,8 +207,15 @@ enum : unsigned { WHERE_SK_PARTIALS = 5 };
 template <int MODE, int CTAS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
-               const __grid_constant__ CUtensorMap tm_b1, const GemmParams p) {
+               const __grid_constant__ CUtensorMap tm_b1, const GemmParams p_in) {
   using Cfg = TileCfg<CTAS>;
+  GemmParams p = p_in;
+  if (p_in.m_dev != nullptr) {
+    const int m = *p_in.m_dev;
+    p.M = m < 0 ? 0 : (m < p_in.M ? m : p_in.M);
+    p.tiles_m = (p.M + Cfg::kTileM - 1) / Cfg::kTileM;
+    p.num_tiles = p.tiles_m * p.tiles_n;
+  }
   constexpr int STAGES = Cfg::kStages;
   constexpr int STAGE_BYTES = Cfg::kStageBytes;
   constexpr int BN_OUT = (MODE == MODE_GATEUP) ? 128 : 256;
@@ -651,7 +661,7 @@ static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b0, con
   p.sk_per = 0;
   p.sk_partials = nullptr;
   p.sk_counters = nullptr;
-  if (CTAS == 1 && sk_ws != nullptr && tuning_int("DF_GEMM_STREAMK", 1) != 0) {
+  if (CTAS == 1 && sk_ws != nullptr && p.m_dev == nullptr && tuning_int("DF_GEMM_STREAMK", 1) != 0) {
     const int waves = (p.num_tiles + units - 1) / units;
     const double eff = static_cast<double>(p.num_tiles) / (static_cast<double>(waves) * units);
     const long long total = static_cast<long long>(p.num_tiles) * p.num_kb;
@@ -708,7 +718,8 @@ static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b0, con
 
 template <int MODE>
 static int launch_gemm(const void* a, const void* b0, const void* b1, void* c, int M, int N, int K, int lda, int ldb,
-                       int ldc, int max_ctas, void* sk_ws, size_t sk_ws_bytes, df_status_t* dev_status, void* stream) {
+                       int ldc, int max_ctas, void* sk_ws, size_t sk_ws_bytes, df_status_t* dev_status, void* stream,
+                       const int* m_dev = nullptr) {
   if (a == nullptr || b0 == nullptr || b1 == nullptr || c == nullptr || dev_status == nullptr)
     return fail(DF_EINVAL, "NULL pointer argument");
   if (M <= 0 || N <= 0 || K <= 0) return fail(DF_EINVAL, "M, N, K must be positive (got %d, %d, %d)", M, N, K);
@@ -742,6 +753,7 @@ static int launch_gemm(const void* a, const void* b0, const void* b1, void* c, i
   p.sk_partials = nullptr;
   p.sk_counters = nullptr;
   p.tile_counter = nullptr;
+  p.m_dev = m_dev;
   p.debug = tuning_int("DF_GEMM_DEBUG", 0);
 
   // One CTA per tile is the default: measured on B200 under the power cap, the CTA-pair
@@ -749,7 +761,7 @@ static int launch_gemm(const void* a, const void* b0, const void* b1, void* c, i
   // (67 % vs 75 % active on a 1024-row gate/up launch), and the two end up within +-3 %.
   // DF_GEMM_CTAS=2 selects the pair variant.
   const int want = tuning_int("DF_GEMM_CTAS", 1);
-  const bool two = want == 2 && M > BM && (max_ctas <= 0 || max_ctas >= 2);
+  const bool two = want == 2 && M > BM && (max_ctas <= 0 || max_ctas >= 2) && m_dev == nullptr;
   if (two)
     return launch_variant<MODE, 2>(tm_a, tm_b0, tm_b1, p, max_ctas, sms, nullptr, 0, static_cast<cudaStream_t>(stream));
   return launch_variant<MODE, 1>(tm_a, tm_b0, tm_b1, p, max_ctas, sms, sk_ws, sk_ws_bytes,
@@ -811,6 +823,22 @@ int df_mlp_gated_bf16(const void* x, const void* w_gate, const void* w_up, const
   int r = df_gateup_silu_bf16_ws(x, w_gate, w_up, h, M, H, I, H, H, I, max_ctas, sk, sk_bytes, dev_status, stream);
   if (r != DF_OK) return r;
   return df_gemm_bf16_ws(h, w_down, out, M, H, I, I, I, H, max_ctas, sk, sk_bytes, dev_status, stream);
+}
+
+int df_mlp_gated_bf16_rows_on_device(const void* x, const void* w_gate, const void* w_up, const void* w_down, void* out,
+                                     void* workspace, int capacity_rows, const int* rows_dev, int H, int I, int max_ctas,
+                                     df_status_t* dev_status, void* stream) {
+  if (workspace == nullptr || rows_dev == nullptr) return df::fail(DF_EINVAL, "workspace or rows_dev is NULL");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return df::fail(DF_EINVAL, "workspace must be 256-byte aligned");
+  if (capacity_rows <= 0 || I <= 0) return df::fail(DF_EINVAL, "capacity_rows and I must be positive");
+  void* h = workspace;
+  void* sk = static_cast<uint8_t*>(workspace) + mlp_h_bytes(capacity_rows, I);
+  const size_t sk_bytes = df_gemm_splitk_workspace_bytes();
+  int r = df::launch_gemm<df::MODE_GATEUP>(x, w_gate, w_up, h, capacity_rows, I, H, H, H, I, max_ctas, sk, sk_bytes,
+                                           dev_status, stream, rows_dev);
+  if (r != DF_OK) return r;
+  return df::launch_gemm<df::MODE_PLAIN>(h, w_down, w_down, out, capacity_rows, H, I, I, I, H, max_ctas, sk, sk_bytes,
+                                         dev_status, stream, rows_dev);
 }
 
 }  // extern "C"

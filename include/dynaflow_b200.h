@@ -178,6 +178,19 @@ int df_comm_region_free(void* dev_ptr);
 int df_allreduce_bf16(const df_comm_rank_t* view, int world, int max_rows, int hidden, int T, int n_ctas,
                       df_status_t* dev_status, void* stream);
 
+/* The two halves on their own, for expert parallelism (the all-gather / reduce-scatter pair the
+ * reference's MoE dispatch and combine are built from, examples/ae/patch/vllm.patch:145-191).
+ * Row slice r = rows [T*r/world, T*(r+1)/world).
+ *   df_all_gather_bf16     : every rank has put ITS slice into its own partial buffer (at the
+ *                            slice's row position); afterwards every rank's sum buffer holds all rows.
+ *   df_reduce_scatter_bf16 : every rank's partial buffer holds T rows of contributions; afterwards
+ *                            rank r's sum buffer holds, in slice r, their sum over ranks (fp32 in
+ *                            rank order, rounded once). */
+int df_all_gather_bf16(const df_comm_rank_t* view, int world, int max_rows, int hidden, int T, int n_ctas,
+                       df_status_t* dev_status, void* stream);
+int df_reduce_scatter_bf16(const df_comm_rank_t* view, int world, int max_rows, int hidden, int T, int n_ctas,
+                           df_status_t* dev_status, void* stream);
+
 /* The fused form: y = sum over ranks of partial; r' = y + residual_in;
  * out = bf16(r' * rsqrt(mean(r'^2) + eps)) * weight; residual_out = r'.
  * Rounding points as in tokenweave.cu:76-103 (bf16 residual, fp32 sum of squares). */
@@ -210,8 +223,40 @@ int df_add_rmsnorm_bf16(const void* y, const void* residual_in, void* residual_o
  * memory. Exercises the flag protocol and the arithmetic without a second GPU.
  * No counterpart in the reference. */
 int df_allreduce_emulated_bf16(const df_comm_rank_t* views, int world, int max_rows, int hidden, int T,
-                               const void* weight, float eps, int fuse_rmsnorm /* 0 none, 1 replicated, 2 sharded residual */,
+                               const void* weight, float eps, int fuse_rmsnorm /* 0 all-reduce, 1 + replicated norm, 2 + sharded-residual norm,
+                                                    3 reduce-scatter, 4 all-gather */,
                                int n_ctas, df_status_t* dev_status, void* stream);
+
+/* -------------------------------------------------------- mixture of experts
+ *
+ * The parts of the reference's dispatch / expert / combine operator triple
+ * (examples/ae/patch/vllm.patch:308-379, 423-527) that are not collectives or GEMMs, for top-2
+ * routing with renormalised softmax weights. Nothing here synchronises with the host: the number
+ * of tokens routed to an expert stays in device memory, where the expert GEMMs read it.
+ */
+
+/* ids[t,0..1] = the two experts with the largest softmax(logits[t,:]) (ties: lower index),
+ * weights[t,0..1] = their probabilities divided by their sum. logits bf16 [T,E]. */
+int df_moe_route_top2(const void* logits, int T, int E, int* ids, float* weights, void* stream);
+
+/* The tokens routed to `expert`, ascending: rows[k] = token, slot[k] = 0/1 (first or second
+ * choice), pos[t] = k or -1, *count_dev = how many. rows/slot need T entries, pos T entries. */
+int df_moe_select_rows(const int* ids, int T, int expert, int* rows, int* slot, int* pos, int* count_dev, void* stream);
+
+/* out[k,:] = x[rows[k],:] for k < *count_dev (bf16, H % 8 == 0; out has `capacity` rows). */
+int df_moe_gather_rows(const void* x, const int* rows, const int* count_dev, int capacity, int H, void* out,
+                       void* stream);
+
+/* contrib[t,:] = bf16(weights[t, slot[pos[t]]] * y[pos[t],:]) where pos[t] >= 0, zeros elsewhere:
+ * this expert's contribution to every token, ready for the reduce-scatter / sum over experts. */
+int df_moe_scatter_rows(const void* y, const int* pos, const int* slot, const float* weights, int T, int H,
+                        void* contrib, void* stream);
+
+/* df_mlp_gated_bf16 over the first *rows_dev rows of x (at most capacity_rows, which also sizes
+ * the workspace: df_mlp_workspace_bytes(capacity_rows, H, I)); rows beyond are not touched. */
+int df_mlp_gated_bf16_rows_on_device(const void* x, const void* w_gate, const void* w_up, const void* w_down, void* out,
+                                     void* workspace, int capacity_rows, const int* rows_dev, int H, int I, int max_ctas,
+                                     df_status_t* dev_status, void* stream);
 
 /* Size of the library-owned scratch behind df_mlp_gated_bf16_static: 64 MiB of
  * static device memory, held by every GPU that loads the library until the

@@ -65,9 +65,10 @@ def allreduce_add_rmsnorm(partials: list[torch.Tensor], residual: torch.Tensor |
 def top2_route(router_logits: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """Mixtral-style routing: softmax over experts in fp32, top-2, renormalise.
     Returns ``(weights [T,2] fp32, expert ids [T,2] int64)``; ties resolve to the
-    lower expert index (``torch.topk`` on CPU)."""
+    lower expert index."""
     probs = torch.softmax(router_logits.float(), dim=-1)
-    w, ids = torch.topk(probs, 2, dim=-1)
+    order = torch.sort(probs, dim=-1, descending=True, stable=True)   # stable: equal values keep index order
+    w, ids = order.values[..., :2], order.indices[..., :2]
     w = w / w.sum(dim=-1, keepdim=True)
     return w, ids
 

@@ -111,6 +111,31 @@ def main() -> None:
         ref = ro[mb * T + lo: mb * T + hi].float()
         assert ((mine - ref).abs().max() / ro.float().abs().max()).item() <= 2e-2, f"rank {rank}: residual slice"
     dist.barrier()
+
+    # ---- expert-parallel top-2 MoE layer: dispatch (all-gather) / expert / combine (reduce-scatter)
+    from dynaflow_b200.moe import ExpertParallelMoE
+
+    E, Hm, Im, per_rank = 8, 256, 512, 96
+    g = torch.Generator().manual_seed(31)
+    xg = torch.randn(per_rank * world, Hm, generator=g).bfloat16()
+    lg = torch.randn(per_rank * world, E, generator=g).bfloat16()
+    mg = (torch.randn(E, Im, Hm, generator=g) * 0.05).bfloat16()
+    mu = (torch.randn(E, Im, Hm, generator=g) * 0.05).bfloat16()
+    md = (torch.randn(E, Hm, Im, generator=g) * 0.05).bfloat16()
+    if E % world == 0:
+        moe = ExpertParallelMoE(Hm, Im, E, per_rank, rank=rank, world=world, weights=(mg, mu, md), slots=1, n_ctas=8,
+                                device=dev)
+        lo = rank * per_rank
+        for _ in range(2):
+            mine = moe.forward(xg[lo:lo + per_rank].to(dev), lg[lo:lo + per_rank].to(dev)).clone()
+        torch.cuda.synchronize()
+        ops.check_status()
+        want_all = ops_oracle.moe_layer(xg, lg, mg, mu, md)
+        rel = ((mine.float().cpu() - want_all[lo:lo + per_rank].float()).abs().max() / want_all.float().abs().max()).item()
+        assert rel <= 2e-2, f"rank {rank}: expert-parallel MoE rel err {rel}"
+        dist.barrier()
+        moe.close()
+    dist.barrier()
     comm.close()
     dist.destroy_process_group()
     if rank == 0:

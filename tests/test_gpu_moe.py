@@ -1,0 +1,165 @@
+"""Top-2 MoE: routing and token movement kernels bit-exact against the oracle, the expert MLP over
+a device-side row count, and the whole layer within the bf16 tolerance."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-2
+
+
+def _rel(got, want):
+    return ((got.float().cpu() - want.float()).abs().max() / want.float().abs().max()).item()
+
+
+@pytest.fixture(scope="module")
+def lib(native_lib):
+    assert torch.cuda.is_available()
+    return native_lib
+
+
+def test_routing_and_selection_are_bit_exact(lib):
+    from oracle import ops_oracle
+
+    g = torch.Generator().manual_seed(0)
+    T, E = 3000, 8
+    logits = torch.randn(T, E, generator=g).bfloat16()
+    logits[5] = logits[5, 0]                      # an all-equal row: ties resolve to the lowest indices
+    logits[7, 3] = logits[7, 6] = 4.0             # a tie for first place
+    want_w, want_ids = ops_oracle.top2_route(logits)
+    dev = logits.cuda()
+    ids = torch.empty(T, 2, dtype=torch.int32, device="cuda")
+    w = torch.empty(T, 2, dtype=torch.float32, device="cuda")
+    assert lib.df_moe_route_top2(dev.data_ptr(), T, E, ids.data_ptr(), w.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(ids.cpu().long(), want_ids)                       # routing: bit-exact
+    assert torch.allclose(w.cpu(), want_w, rtol=1e-5, atol=1e-6)
+    assert ids[5].tolist() == [0, 1] and ids[7].tolist() == [3, 6]
+    rows = torch.empty(T, dtype=torch.int32, device="cuda")
+    slot = torch.empty(T, dtype=torch.int32, device="cuda")
+    pos = torch.empty(T, dtype=torch.int32, device="cuda")
+    count = torch.zeros(1, dtype=torch.int32, device="cuda")
+    total = 0
+    for e in range(E):
+        assert lib.df_moe_select_rows(ids.data_ptr(), T, e, rows.data_ptr(), slot.data_ptr(), pos.data_ptr(),
+                                      count.data_ptr(), None) == 0
+        torch.cuda.synchronize()
+        want_rows, want_slot = torch.nonzero(want_ids == e, as_tuple=True)
+        n = int(count.item())
+        assert n == want_rows.numel()
+        assert torch.equal(rows[:n].cpu().long(), want_rows) and torch.equal(slot[:n].cpu().long(), want_slot)
+        inv = torch.full((T,), -1, dtype=torch.long)
+        inv[want_rows] = torch.arange(n)
+        assert torch.equal(pos.cpu().long(), inv)
+        total += n
+    assert total == 2 * T                                                  # every token went to two experts
+
+
+def test_gather_mlp_scatter_with_device_row_count(lib):
+    from dynaflow_b200 import ops
+    from oracle import ops_oracle
+
+    g = torch.Generator().manual_seed(1)
+    T, H, I = 500, 256, 512
+    x = torch.randn(T, H, generator=g).bfloat16()
+    wg, wu, wd = [(torch.randn(s, generator=g) * 0.05).bfloat16() for s in ((I, H), (I, H), (H, I))]
+    picked = torch.sort(torch.randperm(T, generator=g)[:137]).values
+    rows = torch.zeros(T, dtype=torch.int32)
+    rows[:137] = picked.int()
+    count = torch.tensor([137], dtype=torch.int32)
+    xd, rd, cd = x.cuda(), rows.cuda(), count.cuda()
+    wgd, wud, wdd = wg.cuda(), wu.cuda(), wd.cuda()     # kept alive: the calls below only see raw pointers
+    packed = torch.full((T, H), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert lib.df_moe_gather_rows(xd.data_ptr(), rd.data_ptr(), cd.data_ptr(), T, H, packed.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(packed[:137].cpu(), x[picked])
+    assert torch.isnan(packed[137:].float()).all()                        # rows beyond the count are not touched
+    out = torch.full((T, H), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ws = torch.empty(ops.mlp_workspace_bytes(T, H, I), dtype=torch.uint8, device="cuda")
+    st = ops.status_block()
+    rc = lib.df_mlp_gated_bf16_rows_on_device(packed.data_ptr(), wgd.data_ptr(), wud.data_ptr(), wdd.data_ptr(),
+                                              out.data_ptr(), ws.data_ptr(), T, cd.data_ptr(), H, I, 0, st.data_ptr(), None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = ops_oracle.gated_mlp(x[picked], wg, wu, wd)
+    assert _rel(out[:137], want) <= TOL
+    assert torch.isnan(out[256:].float()).all()                            # tiles past the count never ran
+    # a count of zero is a no-op
+    cd.zero_()
+    out.fill_(float("nan"))
+    lib.df_mlp_gated_bf16_rows_on_device(packed.data_ptr(), wgd.data_ptr(), wud.data_ptr(), wdd.data_ptr(),
+                                         out.data_ptr(), ws.data_ptr(), T, cd.data_ptr(), H, I, 0, st.data_ptr(), None)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.isnan(out.float()).all()
+
+
+@pytest.mark.parametrize("T,H,I,E", [(256, 256, 512, 8), (1000, 512, 1024, 8)])
+def test_single_rank_moe_layer_matches_oracle(lib, T, H, I, E):
+    from dynaflow_b200 import ops
+    from dynaflow_b200.moe import ExpertParallelMoE
+    from oracle import ops_oracle
+
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    logits = torch.randn(T, E, generator=g).bfloat16()
+    w_gate = (torch.randn(E, I, H, generator=g) * 0.05).bfloat16()
+    w_up = (torch.randn(E, I, H, generator=g) * 0.05).bfloat16()
+    w_down = (torch.randn(E, H, I, generator=g) * 0.05).bfloat16()
+    layer = ExpertParallelMoE(H, I, E, T, weights=(w_gate, w_up, w_down), slots=1)
+    got = layer.forward(x.cuda(), logits.cuda()).clone()
+    again = layer.forward(x.cuda(), logits.cuda())
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(got, again)
+    want = ops_oracle.moe_layer(x, logits, w_gate, w_up, w_down)
+    assert _rel(got, want) <= TOL
+
+
+@pytest.mark.parametrize("world,T,H", [(2, 64, 256), (8, 800, 1024), (4, 36, 64)])
+def test_emulated_all_gather_and_reduce_scatter(lib, world, T, H):
+    """The two halves of the all-reduce as collectives of their own (expert parallelism)."""
+    from dynaflow_b200 import ops
+    from dynaflow_b200.comm import EmulatedComm
+    from dynaflow_b200._native import df_comm_rank_t
+
+    g = torch.Generator().manual_seed(3)
+    data = [torch.randn(T, H, generator=g).bfloat16() for _ in range(world)]
+    em = EmulatedComm(world, max_rows=max(T, 64), hidden=H, n_ctas=4)
+
+    def run(code):
+        views = (df_comm_rank_t * world)()
+        for r in range(world):
+            views[r] = em._view(r, em.ptrs)
+        rc = lib.df_allreduce_emulated_bf16(views, world, em.max_rows, H, T, None, 0.0, code, em.n_ctas,
+                                            ops.status_block().data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        ops.check_status()
+
+    # all-gather: rank r contributes its slice of data[r]
+    full = torch.zeros(T, H).bfloat16()
+    for r in range(world):
+        lo, hi = T * r // world, T * (r + 1) // world
+        em.partial(r, T).copy_(data[r])
+        em.result(r, T).zero_()
+        full[lo:hi] = data[r][lo:hi]
+    run(4)
+    for r in range(world):
+        assert torch.equal(em.result(r, T).cpu(), full), r
+    # reduce-scatter: every rank contributes T rows; rank r receives the sum of slice r
+    acc = torch.zeros(T, H)
+    for r in range(world):
+        em.partial(r, T).copy_(data[r])
+        em.result(r, T).zero_()
+        acc += data[r].float()
+    want = acc.bfloat16()
+    run(3)
+    for r in range(world):
+        lo, hi = T * r // world, T * (r + 1) // world
+        got = em.result(r, T).cpu()
+        assert torch.equal(got[lo:hi], want[lo:hi]), r
+        keep = torch.ones(T, dtype=torch.bool)
+        keep[lo:hi] = False
+        assert got[keep].abs().sum() == 0                                   # nothing written outside the own slice
