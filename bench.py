@@ -407,6 +407,81 @@ def m_sweep(layer, dev, peaks) -> list[dict]:
     return out
 
 
+def run_decoder(args) -> None:
+    """Second workload (not the default line): Llama-3-8B-shaped decoder prefill, 8 x 2048 ids, two
+    micro-batches, tensor parallel over the launched ranks. value = tokens/s of the whole stack."""
+    import torch
+    import torch.distributed as dist
+
+    from dynaflow_b200 import ops
+    from dynaflow_b200.decoder import DecoderShape, TensorParallelDecoder
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    shape = DecoderShape(layers=args.layers)
+    batch, seq = 8, 2048
+    dec = TensorParallelDecoder(shape, rank=rank, world=world, max_rows=batch * seq // MICRO_BATCHES,
+                                micro_batches=MICRO_BATCHES, seed=0, device=dev, n_ctas=args.comm_ctas)
+    ids = torch.randint(0, shape.vocab, (batch, seq), generator=torch.Generator().manual_seed(1)).to(dev)
+
+    def timed(**kw):
+        for _ in range(max(2, args.warmup // 2)):
+            dec.forward(ids, **kw)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(3, args.steps // 20)
+        a.record()
+        for _ in range(reps):
+            dec.forward(ids, **kw)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / reps
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    t_all = timed()
+    ops.check_status()
+    line = {"workload": f"Llama-3-8B-shaped decoder prefill, {shape.layers} layers, ids {batch}x{seq}, "
+                        f"{MICRO_BATCHES} micro-batches, tp{world}",
+            "metric": "prefill tokens/sec", "unit": "tokens/s", "n_gpus": world, "ms_per_forward": t_all,
+            "value": batch * seq / (t_all * 1e-3)}
+    peaks, kind = measured_peaks()
+    s = shape
+    linear = 2.0 * (s.hidden * (s.heads + 2 * s.kv_heads) * s.head_dim + s.heads * s.head_dim * s.hidden
+                    + 3 * s.hidden * s.intermediate)
+    attn = 4.0 * ((seq + 1) / 2) * s.heads * s.head_dim
+    flops = (linear + attn) * s.layers * batch * seq
+    line["flops_per_forward"] = flops
+    line["tflops_per_gpu"] = flops / world / (t_all * 1e-3) / 1e12
+    line["frac_of_tensor_peak"] = line["tflops_per_gpu"] / float(peaks["bf16_tflops"])
+    line["peak_source"] = f"{kind} cuBLAS bf16 burst"
+    if world > 1:
+        t_compute = timed(skip_comm=True)
+        t_comm = timed(skip_compute=True)
+        payload = 2 * s.layers * batch * seq * s.hidden * 2
+        line["comm"] = {"ms_overlapped": t_all, "ms_compute_only": t_compute, "ms_comm_only": t_comm,
+                        "hidden_frac": 1.0 - (t_all - t_compute) / t_comm,
+                        "wire_ms_at_770": (world - 1) / world * payload / 770e9 * 1e3,
+                        "roofline_ms": max(flops / world / (float(peaks["bf16_tflops"]) * 1e12),
+                                           (world - 1) / world * payload / 770e9) * 1e3}
+        line["frac_of_roofline"] = line["comm"]["roofline_ms"] / t_all
+    if rank == 0:
+        print(json.dumps(line))
+    dec.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main() -> None:
     global ROWS
     ap = argparse.ArgumentParser()
@@ -419,6 +494,10 @@ def main() -> None:
     ap.add_argument("--comm-ctas", type=int, default=32, help="CTAs of the peer-memory all-reduce kernel (N > 1)")
     ap.add_argument("--replicated-residual", action="store_true",
                     help="N > 1 chain: keep the residual stream replicated on every rank instead of sharded by rows")
+    ap.add_argument("--workload", choices=["mlp", "decoder"], default="mlp",
+                    help="mlp: the fused gated-MLP layer step (the benchmark line); decoder: a Llama-3-8B-shaped "
+                         "decoder prefill on the same kernels (reported separately)")
+    ap.add_argument("--layers", type=int, default=32, help="decoder workload: number of layers")
     ap.add_argument("--fused-norm", action="store_true", help="N > 1 chain: one-launch all-reduce+RMSNorm kernel")
     ap.add_argument("--no-sweep", action="store_true", help="skip the M sweep (profiling runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
@@ -430,6 +509,8 @@ def main() -> None:
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.workload == "decoder":
+        run_decoder(args)
     else:
         run_ours(args)
 

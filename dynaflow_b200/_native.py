@@ -65,6 +65,7 @@ SIGNATURES: dict[str, tuple] = {
     "df_moe_gather_rows": (_i, [_vp, _vp, _vp, _i, _i, _vp, _vp]),
     "df_moe_scatter_rows": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp]),
     "df_mlp_gated_bf16_rows_on_device": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _vp]),
+    "df_rope_bf16": (_i, [_vp, _vp, _i, _i, _i, _i, _f, _vp]),
     "df_allreduce_add_rmsnorm_bf16": (_i, [_rank_p, _i, _i, _i, _i, _vp, _f, _i, _vp, _vp]),
     "df_allreduce_add_rmsnorm_sharded_bf16": (_i, [_rank_p, _i, _i, _i, _i, _vp, _f, _i, _vp, _vp]),
     "df_add_rmsnorm_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _i, _i, _vp]),

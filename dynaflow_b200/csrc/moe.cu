@@ -198,3 +198,60 @@ int df_moe_scatter_rows(const void* y, const int* pos, const int* slot, const fl
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Rotary position embedding, rotate-half convention, in place on the q and k
+// heads of a fused qkv activation [T, (q_heads + 2 * kv_heads) * head_dim]:
+//   (x1, x2) <- (x1 cos - x2 sin, x2 cos + x1 sin) with x1 / x2 the two halves of a head,
+//   angle = pos[t] * theta^(-2i / head_dim), computed in fp32.
+// One thread per (token, head, 8 consecutive dims of the first half).
+namespace df {
+
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ pos, int T, int heads, int head_dim,
+                            int row_stride, float theta) {
+  const int half = head_dim >> 1;
+  const int groups = half >> 3;
+  const long long total = static_cast<long long>(T) * heads * groups;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int gidx = static_cast<int>(i % groups);
+    const int head = static_cast<int>((i / groups) % heads);
+    const int t = static_cast<int>(i / (static_cast<long long>(groups) * heads));
+    __nv_bfloat16* base = qkv + static_cast<size_t>(t) * row_stride + head * head_dim + gidx * 8;
+    uint4 a = *reinterpret_cast<uint4*>(base), b = *reinterpret_cast<uint4*>(base + half);
+    __nv_bfloat16* x1 = reinterpret_cast<__nv_bfloat16*>(&a);
+    __nv_bfloat16* x2 = reinterpret_cast<__nv_bfloat16*>(&b);
+    const float p = static_cast<float>(pos[t]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int d = gidx * 8 + j;
+      const float inv_freq = powf(theta, -2.0f * static_cast<float>(d) / static_cast<float>(head_dim));
+      float s, c;
+      sincosf(p * inv_freq, &s, &c);
+      const float u = __bfloat162float(x1[j]), v = __bfloat162float(x2[j]);
+      x1[j] = __float2bfloat16_rn(u * c - v * s);
+      x2[j] = __float2bfloat16_rn(v * c + u * s);
+    }
+    *reinterpret_cast<uint4*>(base) = a;
+    *reinterpret_cast<uint4*>(base + half) = b;
+  }
+}
+
+}  // namespace df
+
+extern "C" int df_rope_bf16(void* qkv, const int* positions, int T, int heads, int head_dim, int row_stride, float theta,
+                            void* stream) {
+  if (qkv == nullptr || positions == nullptr) return df::fail(DF_EINVAL, "NULL pointer argument");
+  if (T <= 0 || heads <= 0 || head_dim <= 0 || (head_dim % 16) != 0 || (row_stride % 8) != 0 ||
+      row_stride < heads * head_dim)
+    return df::fail(DF_EINVAL, "head_dim must be a multiple of 16 and the row stride cover the rotated heads");
+  if (reinterpret_cast<uintptr_t>(qkv) & 15u) return df::fail(DF_EINVAL, "qkv must be 16-byte aligned");
+  const long long total = static_cast<long long>(T) * heads * (head_dim / 16);
+  int grid = static_cast<int>((total + 255) / 256);
+  int sms = df_sm_count();
+  if (sms <= 0) sms = 148;
+  if (grid > sms * 16) grid = sms * 16;
+  df::rope_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<__nv_bfloat16*>(qkv), positions, T,
+                                                                        heads, head_dim, row_stride, theta);
+  return df::check_launch("rope");
+}

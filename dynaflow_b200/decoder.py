@@ -1,0 +1,233 @@
+"""A Llama-style decoder stack on the batch-split, overlapped schedule, tensor parallel.
+
+Everything on the hot path except the attention core runs on this library's kernels: fused
+qkv projection and output projection (``ops.gemm_bf16``), rotary embedding
+(``df_rope_bf16``), the gated MLP (``ops.gated_mlp``), and between the blocks the
+reduce-scatter / residual add / RMSNorm / all-gather kernel on the communication stream
+(single rank: the stand-alone add + RMSNorm kernel). The attention core is PyTorch's
+``scaled_dot_product_attention``: the reference treats attention as an opaque subgraph as
+well (``examples/ae/scheduler/vllm/nanoflow.py:91-94``).
+
+Schedule: the requests are cut into micro-batches; for every half-block (attention part,
+MLP part) the micro-batches run in order on the compute stream, and the reduction of
+micro-batch ``i`` runs on the communication stream under the GEMMs of micro-batch ``i+1``
+(NanoFlow's round-robin, ``examples/ae/scheduler/hf/nanoflow.py:123-146``, at the granularity
+of the subgraphs its split rules produce).
+
+Sharding (Megatron): q/k/v heads and the MLP intermediate by columns, o and down by rows;
+activations between blocks are replicated, the residual stream is sharded by rows.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+import torch.nn.functional as F
+
+from . import _native, ops
+from .comm import PeerComm, add_rmsnorm
+
+
+@dataclasses.dataclass
+class DecoderShape:
+    hidden: int = 4096
+    intermediate: int = 14336
+    heads: int = 32
+    kv_heads: int = 8
+    head_dim: int = 128
+    layers: int = 32
+    vocab: int = 128256
+    eps: float = 1e-5
+    rope_theta: float = 10000.0
+
+
+class TensorParallelDecoder:
+    def __init__(self, shape: DecoderShape, *, rank: int = 0, world: int = 1, max_rows: int, micro_batches: int = 2,
+                 seed: int = 0, device: torch.device | None = None, weights: dict | None = None, n_ctas: int = 32) -> None:
+        s = shape
+        if s.heads % world or s.kv_heads % world or s.intermediate % world:
+            raise ValueError("heads, kv heads and the intermediate size must divide evenly across ranks")
+        self.s, self.rank, self.world = s, rank, world
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.micro_batches = micro_batches
+        self.max_rows = max_rows
+        self.qh, self.kvh = s.heads // world, s.kv_heads // world
+        self.q_cols, self.kv_cols = self.qh * s.head_dim, self.kvh * s.head_dim
+        self.inter = s.intermediate // world
+        self.lib = _native.load()
+        dev = self.device
+        gen = torch.Generator().manual_seed(seed)
+
+        def full(name, *shp):
+            if weights is not None:
+                return weights[name]
+            return (torch.randn(*shp, generator=gen) * 0.02).bfloat16()
+
+        self.embed = full("embed", s.vocab, s.hidden).to(dev)
+        self.lm_head = full("lm_head", s.vocab, s.hidden).to(dev)
+        self.layers = []
+        r = rank
+        for i in range(s.layers):
+            wq = full(f"l{i}.q", s.heads * s.head_dim, s.hidden)
+            wk = full(f"l{i}.k", s.kv_heads * s.head_dim, s.hidden)
+            wv = full(f"l{i}.v", s.kv_heads * s.head_dim, s.hidden)
+            wo = full(f"l{i}.o", s.hidden, s.heads * s.head_dim)
+            wg = full(f"l{i}.gate", s.intermediate, s.hidden)
+            wu = full(f"l{i}.up", s.intermediate, s.hidden)
+            wd = full(f"l{i}.down", s.hidden, s.intermediate)
+            qs, ks, ms = slice(r * self.q_cols, (r + 1) * self.q_cols), slice(r * self.kv_cols, (r + 1) * self.kv_cols), \
+                slice(r * self.inter, (r + 1) * self.inter)
+            self.layers.append({
+                "wqkv": torch.cat([wq[qs], wk[ks], wv[ks]], 0).contiguous().to(dev),
+                "wo": wo[:, qs].contiguous().to(dev),
+                "wg": wg[ms].contiguous().to(dev), "wu": wu[ms].contiguous().to(dev), "wd": wd[:, ms].contiguous().to(dev),
+                "norm1": (weights[f"l{i}.norm1"] if weights else torch.ones(s.hidden).bfloat16()).to(dev),
+                "norm2": (weights[f"l{i}.norm2"] if weights else torch.ones(s.hidden).bfloat16()).to(dev),
+            })
+        self.final_norm = (weights["final_norm"] if weights else torch.ones(s.hidden).bfloat16()).to(dev)
+        n = micro_batches
+        qkv_cols = self.q_cols + 2 * self.kv_cols
+        self.qkv = [torch.empty(max_rows, qkv_cols, dtype=torch.bfloat16, device=dev) for _ in range(n)]
+        self.attn_out = [torch.empty(max_rows, self.q_cols, dtype=torch.bfloat16, device=dev) for _ in range(n)]
+        self.workspace = [torch.empty(ops.mlp_workspace_bytes(max_rows, s.hidden, self.inter), dtype=torch.uint8,
+                                      device=dev) for _ in range(n)]
+        self.x = [torch.empty(max_rows, s.hidden, dtype=torch.bfloat16, device=dev) for _ in range(n)]
+        self.residual = [torch.empty(max_rows, s.hidden, dtype=torch.bfloat16, device=dev) for _ in range(n)]
+        self.partial_local = [torch.empty(max_rows, s.hidden, dtype=torch.bfloat16, device=dev) for _ in range(n)]
+        self.comm = PeerComm(rank, world, max_rows, s.hidden, slots=n, n_ctas=n_ctas, device=dev) if world > 1 else None
+        self.launch_count = 0
+
+    # ------------------------------------------------------------------ pieces
+    def _partial(self, mb: int, rows: int) -> torch.Tensor:
+        return self.comm.partial(mb, rows) if self.comm is not None else self.partial_local[mb][:rows]
+
+    def _attention_half(self, layer: dict, x: torch.Tensor, mb: int, batch: int, seq: int, pos: torch.Tensor) -> None:
+        s = self.s
+        rows = batch * seq
+        qkv = self.qkv[mb][:rows]
+        ops.gemm_bf16(x, layer["wqkv"], out=qkv)
+        rc = self.lib.df_rope_bf16(qkv.data_ptr(), pos.data_ptr(), rows, self.qh + self.kvh, s.head_dim, qkv.stride(0),
+                                   s.rope_theta, torch.cuda.current_stream(self.device).cuda_stream)
+        if rc != 0:
+            raise RuntimeError(_native.last_error())
+        q = qkv[:, :self.q_cols].view(batch, seq, self.qh, s.head_dim).transpose(1, 2)
+        k = qkv[:, self.q_cols:self.q_cols + self.kv_cols].view(batch, seq, self.kvh, s.head_dim).transpose(1, 2)
+        v = qkv[:, self.q_cols + self.kv_cols:].view(batch, seq, self.kvh, s.head_dim).transpose(1, 2)
+        o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.qh != self.kvh)
+        attn = self.attn_out[mb][:rows]
+        attn.view(batch, seq, self.qh, s.head_dim).copy_(o.transpose(1, 2))
+        ops.gemm_bf16(attn, layer["wo"], out=self._partial(mb, rows))
+        self.launch_count += 3
+
+    def _mlp_half(self, layer: dict, x: torch.Tensor, mb: int, rows: int) -> None:
+        ops.gated_mlp(x, layer["wg"], layer["wu"], layer["wd"], out=self._partial(mb, rows), workspace=self.workspace[mb])
+        self.launch_count += 2
+
+    def _reduce_norm(self, mb: int, rows: int, weight: torch.Tensor, first: bool = False) -> torch.Tensor:
+        """Sum the ranks' partials, add the residual, normalise: the next half-block's input."""
+        self.launch_count += 1
+        if self.comm is None:
+            x = self.x[mb][:rows]
+            add_rmsnorm(self.partial_local[mb][:rows], None if first else self.residual[mb][:rows], weight, x,
+                        self.residual[mb][:rows], self.s.eps)
+            return x
+        return self.comm.all_reduce_add_rmsnorm_sharded(mb, rows, self.residual[mb][:rows], weight, self.s.eps,
+                                                        first=first)
+
+    # ----------------------------------------------------------------- forward
+    def forward(self, ids: torch.Tensor, skip_comm: bool = False, skip_compute: bool = False) -> torch.Tensor:
+        """``ids`` [requests, seq] -> hidden states after the final norm, [requests * seq, hidden],
+        as per-micro-batch views concatenated. Requests are cut evenly into micro-batches.
+        ``skip_comm`` / ``skip_compute`` leave out the reductions, resp. the GEMMs and attention
+        (timing of the two halves of the overlap; the values are then meaningless)."""
+        s = self.s
+        batch, seq = ids.shape
+        n = min(self.micro_batches, batch)
+        cuts = [batch * i // n for i in range(n + 1)]
+        main = torch.cuda.current_stream(self.device)
+        comm_stream = self.comm.stream if self.comm is not None else main
+        pos = torch.arange(seq, device=self.device, dtype=torch.int32).repeat(cuts[1] - cuts[0] + 1)
+        xs: list[torch.Tensor] = []
+        rows_of = []
+        for mb in range(n):
+            b = cuts[mb + 1] - cuts[mb]
+            rows = b * seq
+            rows_of.append((b, rows))
+            emb = self.embed[ids[cuts[mb]:cuts[mb + 1]].reshape(-1)]
+            self.partial_local[mb][:rows].copy_(emb) if self.comm is None else self.comm.partial(mb, rows).copy_(emb)
+            xs.append(None)
+        if self.comm is not None:
+            start = torch.cuda.Event()
+            start.record(main)
+            comm_stream.wait_event(start)
+        done: list = [None] * n
+
+        def reduce_after(mb: int, weight: torch.Tensor, first: bool = False) -> None:
+            rows = rows_of[mb][1]
+            if self.comm is None:
+                xs[mb] = self._reduce_norm(mb, rows, weight, first)
+                return
+            ready = torch.cuda.Event()
+            ready.record(main)
+            if skip_comm:
+                xs[mb] = self.comm.partial(mb, rows)
+                return
+            comm_stream.wait_event(ready)
+            with torch.cuda.stream(comm_stream):
+                xs[mb] = self._reduce_norm(mb, rows, weight, first)
+                ev = torch.cuda.Event()
+                ev.record(comm_stream)
+            done[mb] = ev
+
+        # the embedding is the first residual; with several ranks every rank only contributes 1/world of it
+        for mb in range(n):
+            if self.comm is not None:
+                self.comm.partial(mb, rows_of[mb][1]).mul_(1.0 / self.world)
+            reduce_after(mb, self.layers[0]["norm1"], first=True)
+        for li, layer in enumerate(self.layers):
+            for mb in range(n):
+                if done[mb] is not None:
+                    main.wait_event(done[mb])
+                b, rows = rows_of[mb]
+                if not skip_compute:
+                    self._attention_half(layer, xs[mb], mb, b, seq, pos[:rows])
+                reduce_after(mb, layer["norm2"])
+            nxt = self.layers[li + 1]["norm1"] if li + 1 < len(self.layers) else self.final_norm
+            for mb in range(n):
+                if done[mb] is not None:
+                    main.wait_event(done[mb])
+                if not skip_compute:
+                    self._mlp_half(layer, xs[mb], mb, rows_of[mb][1])
+                reduce_after(mb, nxt)
+        if self.comm is not None:
+            main.wait_stream(comm_stream)
+        return torch.cat([xs[mb] for mb in range(n)], 0)
+
+    def logits_last_token(self, hidden: torch.Tensor, batch: int, seq: int) -> torch.Tensor:
+        """Prefill only needs the logits of each request's last token."""
+        last = hidden.view(batch, seq, -1)[:, -1, :].contiguous()
+        return ops.gemm_bf16(last, self.lm_head)
+
+    def close(self) -> None:
+        if self.comm is not None:
+            self.comm.close()
+
+
+def reference_weights(shape: DecoderShape, seed: int = 0) -> dict:
+    """Full (unsharded) bf16 weights N(0, 0.02) by name, for parity tests."""
+    gen = torch.Generator().manual_seed(seed)
+    s = shape
+    w = {"embed": (torch.randn(s.vocab, s.hidden, generator=gen) * 0.02).bfloat16(),
+         "lm_head": (torch.randn(s.vocab, s.hidden, generator=gen) * 0.02).bfloat16(),
+         "final_norm": (1 + 0.1 * torch.randn(s.hidden, generator=gen)).bfloat16()}
+    for i in range(s.layers):
+        w[f"l{i}.q"] = (torch.randn(s.heads * s.head_dim, s.hidden, generator=gen) * 0.02).bfloat16()
+        w[f"l{i}.k"] = (torch.randn(s.kv_heads * s.head_dim, s.hidden, generator=gen) * 0.02).bfloat16()
+        w[f"l{i}.v"] = (torch.randn(s.kv_heads * s.head_dim, s.hidden, generator=gen) * 0.02).bfloat16()
+        w[f"l{i}.o"] = (torch.randn(s.hidden, s.heads * s.head_dim, generator=gen) * 0.02).bfloat16()
+        w[f"l{i}.gate"] = (torch.randn(s.intermediate, s.hidden, generator=gen) * 0.02).bfloat16()
+        w[f"l{i}.up"] = (torch.randn(s.intermediate, s.hidden, generator=gen) * 0.02).bfloat16()
+        w[f"l{i}.down"] = (torch.randn(s.hidden, s.intermediate, generator=gen) * 0.02).bfloat16()
+        w[f"l{i}.norm1"] = (1 + 0.1 * torch.randn(s.hidden, generator=gen)).bfloat16()
+        w[f"l{i}.norm2"] = (1 + 0.1 * torch.randn(s.hidden, generator=gen)).bfloat16()
+    return w

@@ -258,6 +258,12 @@ int df_mlp_gated_bf16_rows_on_device(const void* x, const void* w_gate, const vo
                                      void* workspace, int capacity_rows, const int* rows_dev, int H, int I, int max_ctas,
                                      df_status_t* dev_status, void* stream);
 
+/* Rotary position embedding (rotate-half), in place on the first `heads` heads of every row of a
+ * fused qkv activation (q heads followed by k heads: pass heads = q_heads + kv_heads); row t is
+ * rotated by positions[t]. Part of the attention subgraph's prologue in a decoder layer. */
+int df_rope_bf16(void* qkv, const int* positions, int T, int heads, int head_dim, int row_stride, float theta,
+                 void* stream);
+
 /* Size of the library-owned scratch behind df_mlp_gated_bf16_static: 64 MiB of
  * static device memory, held by every GPU that loads the library until the
  * process exits. */

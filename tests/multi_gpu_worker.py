@@ -7,6 +7,7 @@ import torch.distributed as dist
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 
 def main() -> None:
@@ -135,6 +136,26 @@ def main() -> None:
         assert rel <= 2e-2, f"rank {rank}: expert-parallel MoE rel err {rel}"
         dist.barrier()
         moe.close()
+    dist.barrier()
+
+    # ---- tensor-parallel decoder stack (attention + MLP halves, reductions overlapped) vs PyTorch
+    from dynaflow_b200.decoder import DecoderShape, TensorParallelDecoder, reference_weights
+    from test_gpu_decoder import load_oracle_model, oracle_hidden
+
+    dshape = DecoderShape(hidden=256, intermediate=512, heads=8, kv_heads=8, head_dim=32, layers=2, vocab=256)
+    dweights = reference_weights(dshape, seed=8)
+    dids = torch.randint(0, dshape.vocab, (4, 64), generator=torch.Generator().manual_seed(9))
+    dec = TensorParallelDecoder(dshape, rank=rank, world=world, max_rows=2 * 64, micro_batches=2, weights=dweights,
+                                device=dev, n_ctas=8)
+    hidden = dec.forward(dids.to(dev))
+    torch.cuda.synchronize()
+    ops.check_status()
+    model = load_oracle_model(dshape, dweights).to(dev)
+    want_h = oracle_hidden(model, dids.to(dev)).reshape(-1, dshape.hidden)
+    rel = ((hidden.float() - want_h.float()).abs().max() / want_h.float().abs().max()).item()
+    assert rel <= 2e-2, f"rank {rank}: TP decoder rel err {rel}"
+    dist.barrier()
+    dec.close()
     dist.barrier()
     comm.close()
     dist.destroy_process_group()
