@@ -56,12 +56,13 @@ class TensorParallelDecoder:
         self.inter = s.intermediate // world
         self.lib = _native.load()
         dev = self.device
-        gen = torch.Generator().manual_seed(seed)
+        # random weights are drawn on the device (same seed => same full matrices on every rank)
+        gen = torch.Generator(device=dev).manual_seed(seed)
 
         def full(name, *shp):
             if weights is not None:
                 return weights[name]
-            return (torch.randn(*shp, generator=gen) * 0.02).bfloat16()
+            return (torch.randn(*shp, generator=gen, device=dev) * 0.02).bfloat16()
 
         self.embed = full("embed", s.vocab, s.hidden).to(dev)
         self.lm_head = full("lm_head", s.vocab, s.hidden).to(dev)
