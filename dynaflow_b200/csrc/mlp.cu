@@ -60,12 +60,28 @@ struct TileCfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 512 /*barriers, tile ring*/;
 };
 
-enum : int { MODE_PLAIN = 0, MODE_GATEUP = 1 };
+enum : int { MODE_PLAIN = 0, MODE_GATEUP = 1, MODE_FUSED = 2 };  // FUSED: gate/up tiles then down tiles, one launch
 enum : unsigned { WHERE_PRODUCER = 1, WHERE_MMA_FULL = 2, WHERE_MMA_TMEM = 3, WHERE_EPILOGUE = 4 };
+
+constexpr int kMaxChunks = 64;
+
+// MODE_FUSED only: the tile index space is a sequence of chunks, each a group of row panels in
+// one phase (0 = gate/up, 1 = down), ordered so that the down tiles of a group come one group
+// behind its gate/up tiles.
+struct FusedChunk {
+  int start;    // first tile index of the chunk
+  int phase;
+  int first_m;  // first row panel of the group
+  int gm;       // row panels in the group
+};
 
 struct GemmParams {
   int M, N, K;  // N = output columns (I in GATEUP mode)
   int ldc;
+  // MODE_FUSED, phase 1 (down projection): C2[M, N2] = h[M, K2] * w_down[N2, K2]^T
+  int N2, ldc2, num_kb2, tiles_n2, n_chunks;
+  __nv_bfloat16* C2;
+  unsigned int* panel_done;  // [tiles_m] gate/up tiles finished per row panel, zero at launch
   int tiles_m, tiles_n, num_tiles, num_kb, group_m;
   // Stream-K (1-CTA tiles only; sk_per == 0 means off): the launch's k-blocks, tile after
   // tile, are cut into equal ranges of sk_per units, one range per CTA, so that every SM
@@ -81,6 +97,7 @@ struct GemmParams {
   // processes min(*m_dev, M) rows and M is the capacity the tensor maps were built for.
   const int* m_dev;
   int debug;  // development only: bit 0 = producer skips the copies, bit 1 = epilogue skips the stores
+  FusedChunk chunks[kMaxChunks];
   unsigned long long timeout_ns;
   __nv_bfloat16* C;
   Status* status;
@@ -89,12 +106,12 @@ struct GemmParams {
 // Tile order: groups of `group_m` row panels; inside a group the row panel
 // varies fastest, so the CTAs of one wave share few distinct A and B tiles
 // and those stay in L2, and the weights stream from HBM once per group.
-__device__ __forceinline__ void tile_coords(const GemmParams& p, int t, int& m_blk, int& n_blk) {
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int tiles_m, int t, int& m_blk, int& n_blk) {
   const int per_group = p.group_m * p.tiles_n;
   const int group = t / per_group;
   const int within = t - group * per_group;
   const int first_m = group * p.group_m;
-  const int gm = min(p.group_m, p.tiles_m - first_m);
+  const int gm = min(p.group_m, tiles_m - first_m);
   m_blk = first_m + within % gm;
   n_blk = within / gm;
 }
@@ -109,7 +126,20 @@ __device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(_
 // One stretch of consecutive k-blocks of one tile, processed by one CTA (or CTA pair).
 struct Segment {
   int tile, kb0, kb1;
+  int phase;         // MODE_FUSED: 0 = gate/up tile, 1 = down tile; otherwise 0
+  int m_blk, n_blk;  // tile coordinates
 };
+
+// MODE_FUSED: tile index -> (phase, row panel, column tile); `hint` caches the chunk.
+__device__ __forceinline__ void fused_coords(const GemmParams& p, int t, int& hint, Segment& s) {
+  while (hint + 1 < p.n_chunks && t >= p.chunks[hint + 1].start) ++hint;
+  while (hint > 0 && t < p.chunks[hint].start) --hint;
+  const FusedChunk& c = p.chunks[hint];
+  const int within = t - c.start;
+  s.phase = c.phase;
+  s.m_blk = c.first_m + within % c.gm;
+  s.n_blk = within / c.gm;
+}
 
 constexpr int kSchedSlots = 4;
 enum : int { ROLE_PRODUCER = 0, ROLE_MMA = 1, ROLE_EPILOGUE = 2 };
@@ -128,18 +158,25 @@ struct SchedRing {
 // Stream-K: the units [unit * sk_per, (unit + 1) * sk_per) of the tile-major k-block sequence,
 // cut at tile boundaries. All three warp roles walk the same sequence.
 struct SegmentIter {
-  int cur, end, step, num_kb, num_tiles, iter, first, grid;
-  bool streamk, dynamic;
-  __device__ SegmentIter(const GemmParams& p, int unit, int num_units) {
+  int cur, end, step, num_kb, num_tiles, tiles_m, iter, first, grid, hint;
+  bool streamk, dynamic, fused;
+  const GemmParams* gp;
+  // rows_tiles_m / rows_num_tiles: the tile grid of the rows actually present (device-side row count)
+  __device__ SegmentIter(const GemmParams& p, int rows_tiles_m, int rows_num_tiles, int unit, int num_units,
+                         bool is_fused) {
+    gp = &p;
+    fused = is_fused;
+    hint = 0;
     num_kb = p.num_kb;
-    num_tiles = p.num_tiles;
+    tiles_m = rows_tiles_m;
+    num_tiles = rows_num_tiles;
     streamk = p.sk_per > 0;
     dynamic = !streamk && p.tile_counter != nullptr;
     iter = 0;
     first = unit;
     grid = num_units;
     if (streamk) {
-      const long long total = static_cast<long long>(p.num_tiles) * p.num_kb;
+      const long long total = static_cast<long long>(rows_num_tiles) * p.num_kb;
       const long long b = static_cast<long long>(unit) * p.sk_per;
       const long long e = b + p.sk_per;
       cur = static_cast<int>(b < total ? b : total);
@@ -147,8 +184,25 @@ struct SegmentIter {
       step = 0;
     } else {
       cur = unit;
-      end = p.num_tiles;
+      end = rows_num_tiles;
       step = num_units;
+    }
+  }
+  // fills phase, coordinates and (for whole tiles) the k range of segment s from s.tile
+  __device__ __forceinline__ void locate(Segment& s, bool whole) {
+    if (fused) {
+      fused_coords(*gp, s.tile, hint, s);
+      if (whole) {
+        s.kb0 = 0;
+        s.kb1 = s.phase ? gp->num_kb2 : num_kb;
+      }
+    } else {
+      s.phase = 0;
+      tile_coords(*gp, tiles_m, s.tile, s.m_blk, s.n_blk);
+      if (whole) {
+        s.kb0 = 0;
+        s.kb1 = num_kb;
+      }
     }
   }
   // ROLE_PRODUCER and ROLE_MMA: called by one thread. ROLE_EPILOGUE: by whole warps.
@@ -180,8 +234,7 @@ struct SegmentIter {
       ++iter;
       if (t < 0) return false;
       s.tile = t;
-      s.kb0 = 0;
-      s.kb1 = num_kb;
+      locate(s, true);
       return true;
     }
     if (cur >= end) return false;
@@ -192,11 +245,11 @@ struct SegmentIter {
       const int stop = tile_end < end ? tile_end : end;
       s.kb1 = s.kb0 + (stop - cur);
       cur = stop;
+      locate(s, false);
     } else {
       s.tile = cur;
-      s.kb0 = 0;
-      s.kb1 = num_kb;
       cur += step;
+      locate(s, true);
     }
     return true;
   }
@@ -207,19 +260,21 @@ enum : unsigned { WHERE_SK_PARTIALS = 5 };
 template <int MODE, int CTAS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
-               const __grid_constant__ CUtensorMap tm_b1, const GemmParams p_in) {
+               const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_a2,
+               const __grid_constant__ CUtensorMap tm_b2, const GemmParams p_in) {
   using Cfg = TileCfg<CTAS>;
-  GemmParams p = p_in;
-  if (p_in.m_dev != nullptr) {
-    const int m = *p_in.m_dev;
-    p.M = m < 0 ? 0 : (m < p_in.M ? m : p_in.M);
-    p.tiles_m = (p.M + Cfg::kTileM - 1) / Cfg::kTileM;
-    p.num_tiles = p.tiles_m * p.tiles_n;
+  constexpr bool FUSED = MODE == MODE_FUSED;
+  const GemmParams& p = p_in;
+  // rows actually present: the host's M, or what the device-side count says (at most M)
+  int rows_m = p.M, rows_tiles_m = p.tiles_m, rows_num_tiles = p.num_tiles;
+  if (!FUSED && p.m_dev != nullptr) {
+    const int m = *p.m_dev;
+    rows_m = m < 0 ? 0 : (m < p.M ? m : p.M);
+    rows_tiles_m = (rows_m + Cfg::kTileM - 1) / Cfg::kTileM;
+    rows_num_tiles = rows_tiles_m * p.tiles_n;
   }
   constexpr int STAGES = Cfg::kStages;
   constexpr int STAGE_BYTES = Cfg::kStageBytes;
-  constexpr int BN_OUT = (MODE == MODE_GATEUP) ? 128 : 256;
-
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -259,6 +314,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_b0);
     tma_prefetch_desc(&tm_b1);
+    if (FUSED) {
+      tma_prefetch_desc(&tm_a2);
+      tma_prefetch_desc(&tm_b2);
+    }
   }
   if (warp == 2) {
     if (CTAS == 2) {
@@ -288,15 +347,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      SegmentIter segs(p, unit, num_units);
+      SegmentIter segs(p, rows_tiles_m, rows_num_tiles, unit, num_units, FUSED);
       Segment sg;
       while (ok && segs.next<ROLE_PRODUCER>(sg, ring, dl, 0)) {
         const int t = sg.tile;
-        int m_blk, n_blk;
-        tile_coords(p, t, m_blk, n_blk);
-        const int m0 = m_blk * Cfg::kTileM + static_cast<int>(cta_rank) * BM;
-        const int n0 = n_blk * BN_OUT;
-        const int y1_1cta = (MODE == MODE_GATEUP) ? n0 : n0 + 128;
+        // per-tile operator: compile-time except in the fused launch
+        const int tmode = FUSED ? (sg.phase ? MODE_PLAIN : MODE_GATEUP) : MODE;
+        const int bn_out = (tmode == MODE_GATEUP) ? 128 : 256;
+        const int m0 = sg.m_blk * Cfg::kTileM + static_cast<int>(cta_rank) * BM;
+        const int n0 = sg.n_blk * bn_out;
+        const int y1_1cta = (tmode == MODE_GATEUP) ? n0 : n0 + 128;
+        const CUtensorMap* map_a = (FUSED && sg.phase) ? &tm_a2 : &tm_a;
+        const CUtensorMap* map_b0 = (FUSED && sg.phase) ? &tm_b2 : &tm_b0;
+        const CUtensorMap* map_b1 = (tmode == MODE_GATEUP) ? &tm_b1 : map_b0;
+        if (FUSED && sg.phase) {
+          // the down tile reads the intermediate rows of its panel: wait until every gate/up tile
+          // of that panel has published them (they were handed out before this tile)
+          const unsigned need = static_cast<unsigned>(p.tiles_n);
+          uint32_t spins = 0;
+          while (ld_acquire_gpu(p.panel_done + sg.m_blk) < need) {
+            if ((++spins & 0xffu) == 0u) {
+              if (*dl.abort) {
+                ok = false;
+                break;
+              }
+              if (globaltimer_ns() > dl.t_end) {
+                *dl.abort = 1u;
+                report(dl.status, 1u, 7u, static_cast<unsigned>(t));
+                ok = false;
+                break;
+              }
+            }
+          }
+          if (!ok) break;
+          fence_proxy_async_global();  // those rows were written with ordinary stores, TMA reads them
+        }
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, dl, WHERE_PRODUCER, t)) {
             ok = false;
@@ -309,19 +394,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           } else if (CTAS == 2) {
             // this CTA's half of B: gate rows on the leader, up rows on its peer (GATEUP);
             // B rows [n0, n0+128) on the leader and [n0+128, n0+256) on its peer (PLAIN)
-            const CUtensorMap* map_b = (MODE == MODE_GATEUP && cta_rank == 1) ? &tm_b1 : &tm_b0;
-            const int yb = (MODE == MODE_GATEUP) ? n0 : n0 + static_cast<int>(cta_rank) * 128;
+            const CUtensorMap* map_b = (tmode == MODE_GATEUP && cta_rank == 1) ? &tm_b1 : &tm_b0;
+            const int yb = (tmode == MODE_GATEUP) ? n0 : n0 + static_cast<int>(cta_rank) * 128;
             // both CTAs' bytes are counted on the leader's barrier, which the MMA thread waits on
             const uint32_t bar = mapa_shared(smem_u32(&full[stage]), 0u);
             if (cta_rank == 0) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);
             tma_load_2d_2cta(sa, &tm_a, bar, kb * BK, m0);
             tma_load_2d_2cta(sb, map_b, bar, kb * BK, yb);
           } else {
-            const CUtensorMap* map1 = (MODE == MODE_GATEUP) ? &tm_b1 : &tm_b0;
             mbar_expect_tx(&full[stage], STAGE_BYTES);
-            tma_load_2d(sa, &tm_a, &full[stage], kb * BK, m0);
-            tma_load_2d(sb, &tm_b0, &full[stage], kb * BK, n0);
-            tma_load_2d(sb + B_HALF_BYTES, map1, &full[stage], kb * BK, y1_1cta);
+            tma_load_2d(sa, map_a, &full[stage], kb * BK, m0);
+            tma_load_2d(sb, map_b0, &full[stage], kb * BK, n0);
+            tma_load_2d(sb + B_HALF_BYTES, map_b1, &full[stage], kb * BK, y1_1cta);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -339,7 +423,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      SegmentIter segs(p, unit, num_units);
+      SegmentIter segs(p, rows_tiles_m, rows_num_tiles, unit, num_units, FUSED);
       Segment sg;
       for (; ok && segs.next<ROLE_MMA>(sg, ring, dl, 0); ++it) {
         const int t = sg.tile;
@@ -398,15 +482,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     // ---------------------------------------------------------- epilogue
     const int q = warp - 4;  // == warp % 4: the TMEM lane quarter this warp may read
     int it = 0;
-    SegmentIter segs(p, unit, num_units);
+    SegmentIter segs(p, rows_tiles_m, rows_num_tiles, unit, num_units, FUSED);
     Segment sg;
     for (; segs.next<ROLE_EPILOGUE>(sg, ring, dl, lane); ++it) {
       const int t = sg.tile;
-      int m_blk, n_blk;
-      tile_coords(p, t, m_blk, n_blk);
-      const int n0 = n_blk * BN_OUT;
+      const int tmode = FUSED ? (sg.phase ? MODE_PLAIN : MODE_GATEUP) : MODE;
+      const int m_blk = sg.m_blk;
+      const int n0 = sg.n_blk * ((tmode == MODE_GATEUP) ? 128 : 256);
       const int row_in_tile = q * 32 + lane;
       const int row = m_blk * Cfg::kTileM + static_cast<int>(cta_rank) * BM + row_in_tile;
+      __nv_bfloat16* const c_base = (FUSED && sg.phase) ? p.C2 : p.C;
+      const int c_ld = (FUSED && sg.phase) ? p.ldc2 : p.ldc;
+      const int c_cols = (FUSED && sg.phase) ? p.N2 : p.N;
       const int acc = it & 1;
       const uint32_t aphase = (it >> 1) & 1u;
       bool ok = mbar_wait(&tfull[acc], aphase, dl, WHERE_EPILOGUE, t);
@@ -414,8 +501,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       if (!ok) break;
       tc_fence_after();
       const uint32_t t_acc = tmem_base + static_cast<uint32_t>(acc * ACC_COLS) + (static_cast<uint32_t>(q * 32) << 16);
-      __nv_bfloat16* crow = p.C + static_cast<size_t>(row) * p.ldc;
-      const bool row_ok = row < p.M && !(p.debug & 2);
+      __nv_bfloat16* crow = c_base + static_cast<size_t>(row) * c_ld;
+      const bool row_ok = row < rows_m && !(p.debug & 2);
 
       // ---- stream-K: a segment that does not start at k = 0 only delivers its fp32 partial
       // sums; the CTA that owns the tile's first k-blocks (it reaches them last) adds the
@@ -429,7 +516,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             uint32_t r[32];
             tmem_ld_32x32(t_acc + c * 32, r);
             tmem_ld_wait();
-            if (row < p.M) {
+            if (row < rows_m) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) mine[(c * 32 + j) * BM + row_in_tile] = __uint_as_float(r[j]);
             }
@@ -467,7 +554,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             uint32_t r[32];
             tmem_ld_32x32(t_acc + c * 32, r);
             tmem_ld_wait();
-            if (row < p.M) {
+            if (row < rows_m) {
 #pragma unroll 1  // (unrolling costs 32 registers, which the co-resident reduction kernel needs)
               for (int o2 = 1; o2 <= sk_others; ++o2) {
                 const float* part = p.sk_partials + static_cast<size_t>(unit + o2) * (ACC_COLS * BM) + row_in_tile;
@@ -482,7 +569,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         }
       }
 
-      if (MODE == MODE_GATEUP) {
+      if (tmode == MODE_GATEUP) {
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t g[32], u[32];
@@ -504,7 +591,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const int col = n0 + c * 32;
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
-              if (col + v * 8 < p.N) {
+              if (col + v * 8 < c_cols) {
                 *reinterpret_cast<uint4*>(crow + col + v * 8) =
                     make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
               }
@@ -524,13 +611,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             const int col = n0 + c * 32;
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
-              if (col + v * 8 < p.N) {
+              if (col + v * 8 < c_cols) {
                 *reinterpret_cast<uint4*>(crow + col + v * 8) =
                     make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
               }
             }
           }
         }
+      }
+      if (FUSED && sg.phase == 0) {
+        // publish this tile's rows of the intermediate: all 128 threads' stores, then one count
+        __threadfence();
+        fence_proxy_async_global();
+        epilogue_bar_sync();
+        if (threadIdx.x == 4 * 32) atomicAdd(p.panel_done + m_blk, 1u);
       }
       tc_fence_before();
       if (CTAS == 2) {
@@ -641,6 +735,7 @@ static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b0, con
                           int max_ctas, int sms, void* sk_ws, size_t sk_ws_bytes, cudaStream_t stream) {
   using Cfg = TileCfg<CTAS>;
   constexpr int BN_OUT = (MODE == MODE_GATEUP) ? 128 : 256;
+  static_assert(MODE != MODE_FUSED, "the fused launch has its own host path");
   // the attribute is per device; setting it on every call is cheap and covers every device that launches
   const cudaError_t attr_err =
       cudaFuncSetAttribute(gemm_tc_kernel<MODE, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
@@ -708,10 +803,100 @@ static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b0, con
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<MODE, CTAS>, tm_a, tm_b0, tm_b1, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<MODE, CTAS>, tm_a, tm_b0, tm_b1, tm_a, tm_b0, p);
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
     return fail(DF_ECUDA, "gemm launch (%d-CTA tiles): %s", CTAS, cudaGetErrorString(e));
+  }
+  return DF_OK;
+}
+
+// out = (silu(x wg^T) (.) (x wu^T)) wd^T as ONE persistent launch: gate/up tiles and down tiles in
+// one dynamically handed-out tile sequence; a down tile waits for its row panel's gate/up tiles
+// through a per-panel counter. Needs the workspace (tile counter, panel counters).
+static int launch_fused_mlp(const void* x, const void* wg, const void* wu, void* h, const void* wd, void* out, int M,
+                            int H, int I, int max_ctas, void* sk_ws, size_t sk_ws_bytes, df_status_t* dev_status,
+                            cudaStream_t stream) {
+  const int sms = df_sm_count();
+  if (sms <= 0) return fail(DF_ECUDA, "no CUDA device");
+  using Cfg = TileCfg<1>;
+  const cudaError_t attr_err = cudaFuncSetAttribute(gemm_tc_kernel<MODE_FUSED, 1>,
+                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  if (attr_err != cudaSuccess) return fail(DF_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(attr_err));
+  CUtensorMap tm_x, tm_g, tm_u, tm_h, tm_d;
+  if (!make_map_bf16(&tm_x, x, M, H, H, BM)) return DF_ECUDA;
+  if (!make_map_bf16(&tm_g, wg, I, H, H, 128)) return DF_ECUDA;
+  if (!make_map_bf16(&tm_u, wu, I, H, H, 128)) return DF_ECUDA;
+  if (!make_map_bf16(&tm_h, h, M, I, I, BM)) return DF_ECUDA;
+  if (!make_map_bf16(&tm_d, wd, H, I, I, 128)) return DF_ECUDA;
+
+  GemmParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.M = M;
+  p.N = I;
+  p.K = H;
+  p.ldc = I;
+  p.C = static_cast<__nv_bfloat16*>(h);
+  p.N2 = H;
+  p.ldc2 = H;
+  p.C2 = static_cast<__nv_bfloat16*>(out);
+  p.num_kb = (H + BK - 1) / BK;
+  p.num_kb2 = (I + BK - 1) / BK;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (I + 127) / 128;
+  p.tiles_n2 = (H + 255) / 256;
+  p.num_tiles = p.tiles_m * (p.tiles_n + p.tiles_n2);
+  p.timeout_ns = timeout_ns();
+  p.status = reinterpret_cast<Status*>(dev_status);
+  p.debug = tuning_int("DF_GEMM_DEBUG", 0);
+  int g = tuning_int("DF_GEMM_GROUP_M", 32);
+  if (g < 1) g = 1;
+  while (2 * ((p.tiles_m + g - 1) / g) > kMaxChunks) g *= 2;
+  p.group_m = g;
+  // chunk order: up(0), up(1), down(0), up(2), down(1), ..., down(last): a group's down tiles come one
+  // group behind its gate/up tiles, so their inputs are long finished when they are handed out
+  const int groups = (p.tiles_m + g - 1) / g;
+  int start = 0, n = 0;
+  auto add = [&](int phase, int grp) {
+    const int first_m = grp * g;
+    const int gm = (p.tiles_m - first_m) < g ? (p.tiles_m - first_m) : g;
+    p.chunks[n].start = start;
+    p.chunks[n].phase = phase;
+    p.chunks[n].first_m = first_m;
+    p.chunks[n].gm = gm;
+    start += gm * (phase ? p.tiles_n2 : p.tiles_n);
+    ++n;
+  };
+  for (int grp = 0; grp < groups; ++grp) {
+    add(0, grp);
+    if (grp >= 1) add(1, grp - 1);
+  }
+  add(1, groups - 1);
+  p.n_chunks = n;
+
+  if (sk_ws == nullptr || sk_ws_bytes < kSkCounterBytes || static_cast<size_t>(p.tiles_m) * 4 > kSkCounterBytes - 64)
+    return fail(DF_EINVAL, "the fused MLP launch needs the workspace for its tile and panel counters");
+  p.panel_done = static_cast<unsigned int*>(sk_ws);
+  p.tile_counter = reinterpret_cast<unsigned int*>(static_cast<uint8_t*>(sk_ws) + kSkCounterBytes - 64);
+  cudaError_t me = cudaMemsetAsync(p.panel_done, 0, static_cast<size_t>(p.tiles_m) * 4, stream);
+  if (me == cudaSuccess) me = cudaMemsetAsync(p.tile_counter, 0, 4, stream);
+  if (me != cudaSuccess) return fail(DF_ECUDA, "counter reset: %s", cudaGetErrorString(me));
+
+  int units = sms;
+  if (max_ctas > 0 && max_ctas < units) units = max_ctas;
+  if (p.num_tiles < units) units = p.num_tiles;
+  if (tuning_int("DF_DEBUG", 0) > 0)
+    std::fprintf(stderr, "[df] fused mlp M=%d H=%d I=%d tiles=%d grid=%d group_m=%d chunks=%d\n", M, H, I, p.num_tiles,
+                 units, p.group_m, p.n_chunks);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(units, 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<MODE_FUSED, 1>, tm_x, tm_g, tm_u, tm_h, tm_d, p);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(DF_ECUDA, "fused MLP launch: %s", cudaGetErrorString(e));
   }
   return DF_OK;
 }
@@ -820,6 +1005,20 @@ int df_mlp_gated_bf16(const void* x, const void* w_gate, const void* w_up, const
   void* h = workspace;
   void* sk = static_cast<uint8_t*>(workspace) + mlp_h_bytes(M, I);
   const size_t sk_bytes = df_gemm_splitk_workspace_bytes();
+  // One persistent launch for both GEMMs once there is more than a wave of gate/up tiles and the
+  // down projection has enough tiles to fill the SMs (below that the stream-K forms of the two
+  // separate launches do better); DF_MLP_FUSED=0 disables it.
+  const int sms = df_sm_count();
+  const int units = (max_ctas > 0 && max_ctas < sms) ? max_ctas : sms;
+  const long long up_tiles = static_cast<long long>((M + 127) / 128) * ((I + 127) / 128);
+  const long long down_tiles = static_cast<long long>((M + 127) / 128) * ((H + 127) / 128);
+  const bool down_wants_stream_k = down_tiles <= units && down_tiles * 10 < static_cast<long long>(units) * 6;
+  if (sms > 0 && up_tiles > units && !down_wants_stream_k && df::tuning_int("DF_MLP_FUSED", 1) != 0 && (H % 8) == 0 && (I % 8) == 0 &&
+      x != nullptr && w_gate != nullptr && w_up != nullptr && w_down != nullptr && out != nullptr &&
+      dev_status != nullptr && df::aligned16(x) && df::aligned16(w_gate) && df::aligned16(w_up) &&
+      df::aligned16(w_down) && df::aligned16(out))
+    return df::launch_fused_mlp(x, w_gate, w_up, h, w_down, out, M, H, I, max_ctas, sk, sk_bytes, dev_status,
+                                static_cast<cudaStream_t>(stream));
   int r = df_gateup_silu_bf16_ws(x, w_gate, w_up, h, M, H, I, H, H, I, max_ctas, sk, sk_bytes, dev_status, stream);
   if (r != DF_OK) return r;
   return df_gemm_bf16_ws(h, w_down, out, M, H, I, I, I, H, max_ctas, sk, sk_bytes, dev_status, stream);

@@ -188,3 +188,34 @@ def test_small_m_stream_k_path(ops, M, H, I):
         os.environ["DF_GEMM_STREAMK"] = "1"
     ops.check_status()
     assert rel_err(out3, out1) <= 1e-2
+
+
+@pytest.mark.parametrize("M,H,I", [(256, 4096, 14336), (1000, 1024, 2816), (4096, 4096, 14336), (8192, 4096, 1792)])
+def test_one_launch_mlp_equals_two_launches(ops, M, H, I):
+    """df_mlp_gated_bf16 runs gate/up and down as ONE persistent launch (down tiles wait on
+    per-panel counters for their rows of the intermediate). Same tiles, same accumulation
+    order: the result must be bit-identical to the two separate launches, every time."""
+    import os
+
+    g = torch.Generator(device="cuda").manual_seed(M + I)
+    x = torch.randn(M, H, device="cuda", generator=g).bfloat16()
+    wg = (torch.randn(I, H, device="cuda", generator=g) * 0.02).bfloat16()
+    wu = (torch.randn(I, H, device="cuda", generator=g) * 0.02).bfloat16()
+    wd = (torch.randn(H, I, device="cuda", generator=g) * 0.02).bfloat16()
+    os.environ["DF_MLP_FUSED"] = "0"
+    os.environ["DF_GEMM_STREAMK"] = "0"      # whole tiles, as the single launch computes them
+    try:
+        two = ops.gated_mlp(x, wg, wu, wd)
+    finally:
+        os.environ["DF_MLP_FUSED"] = "1"
+        os.environ["DF_GEMM_STREAMK"] = "1"
+    for _ in range(5):
+        one = ops.gated_mlp(x, wg, wu, wd)
+        if ((M + 127) // 128) * ((H + 127) // 128) >= 128:   # fewer down tiles take the stream-K path
+            assert torch.equal(one, two)
+        else:
+            assert rel_err(one, two) <= 1e-2
+    ops.check_status()
+    small = ops.gated_mlp(x, wg, wu, wd, max_ctas=5)     # few CTAs: long waits on the panel counters
+    ops.check_status()
+    assert torch.equal(small, two)
