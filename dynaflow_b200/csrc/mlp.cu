@@ -60,6 +60,19 @@ struct TileCfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 512 /*barriers, tile ring*/;
 };
 
+// 1-CTA tiles take their stage geometry at run time: a launch with at most 64 rows of A copies
+// only 16, 32 or 64 of them per stage (the MMA still spans 128 accumulator rows; the rows
+// beyond the box read whatever follows in the stage, and are never stored), which leaves room
+// for more stages -- more weight bytes in flight per SM, the quantity that bounds a launch
+// that streams the weights once.
+constexpr int kMaxSmemBytes = 227 * 1024;
+constexpr int kMaxStages = 12;
+static inline int stage_bytes_for(int a_rows) { return a_rows * BK * 2 + 2 * B_HALF_BYTES; }
+static inline int stages_for(int a_rows) {
+  int n = (kMaxSmemBytes - 1024 - 512) / stage_bytes_for(a_rows);
+  return n > kMaxStages ? kMaxStages : n;
+}
+
 enum : int { MODE_PLAIN = 0, MODE_GATEUP = 1, MODE_FUSED = 2 };  // FUSED: gate/up tiles then down tiles, one launch
 enum : unsigned { WHERE_PRODUCER = 1, WHERE_MMA_FULL = 2, WHERE_MMA_TMEM = 3, WHERE_EPILOGUE = 4 };
 
@@ -97,6 +110,11 @@ struct GemmParams {
   // processes min(*m_dev, M) rows and M is the capacity the tensor maps were built for.
   const int* m_dev;
   int debug;  // development only: bit 0 = producer skips the copies, bit 1 = epilogue skips the stores
+  // 1-CTA tiles: a_rows = rows of A a stage has room for (a multiple of 16, at most 128), a_tx =
+  // bytes one copy of A delivers (its box has exactly the launch's rows when there are fewer than
+  // 128, so that no copy runs past the matrix: such rows cost a measured 0.3 us per k-block),
+  // stages = pipeline depth.
+  int a_rows, a_tx, stages;
   FusedChunk chunks[kMaxChunks];
   unsigned long long timeout_ns;
   __nv_bfloat16* C;
@@ -257,7 +275,13 @@ struct SegmentIter {
 
 enum : unsigned { WHERE_SK_PARTIALS = 5 };
 
-template <int MODE, int CTAS>
+// SKINNY (at most 64 rows of A, 1-CTA tiles, stream-K or whole tiles): the operands swap roles
+// in the MMA. The 128 weight rows of each half of the B stage span the accumulator's lanes and
+// the a_rows rows of A its columns, D0 = B0 * A^T in columns [0, a_rows) and D1 = B1 * A^T in
+// [a_rows, 2 a_rows). All 128 epilogue threads then own one output column each and a few values
+// per row of A, so folding the stream-K partial sums takes a handful of loads per thread
+// instead of a chain of 256-column sweeps by the few threads that own valid rows.
+template <int MODE, int CTAS, bool SKINNY = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b0,
                const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_a2,
@@ -273,8 +297,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     rows_tiles_m = (rows_m + Cfg::kTileM - 1) / Cfg::kTileM;
     rows_num_tiles = rows_tiles_m * p.tiles_n;
   }
-  constexpr int STAGES = Cfg::kStages;
-  constexpr int STAGE_BYTES = Cfg::kStageBytes;
+  const int STAGES = (CTAS == 2) ? Cfg::kStages : p.stages;
+  const int A_STAGE_BYTES = (CTAS == 2) ? A_BYTES : p.a_rows * (BK * 2);
+  const int STAGE_BYTES = (CTAS == 2) ? Cfg::kStageBytes : A_STAGE_BYTES + 2 * B_HALF_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t* smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -388,7 +413,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             break;
           }
           uint8_t* sa = smem + stage * STAGE_BYTES;
-          uint8_t* sb = sa + A_BYTES;
+          uint8_t* sb = sa + A_STAGE_BYTES;
           if (p.debug & 1) {
             if (cta_rank == 0) mbar_arrive(&full[stage]);
           } else if (CTAS == 2) {
@@ -402,7 +427,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             tma_load_2d_2cta(sa, &tm_a, bar, kb * BK, m0);
             tma_load_2d_2cta(sb, map_b, bar, kb * BK, yb);
           } else {
-            mbar_expect_tx(&full[stage], STAGE_BYTES);
+            mbar_expect_tx(&full[stage], p.a_tx + 2 * B_HALF_BYTES);
             tma_load_2d(sa, map_a, &full[stage], kb * BK, m0);
             tma_load_2d(sb, map_b0, &full[stage], kb * BK, n0);
             tma_load_2d(sb + B_HALF_BYTES, map_b1, &full[stage], kb * BK, y1_1cta);
@@ -440,11 +465,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           tc_fence_after();
           const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
           const uint64_t da = make_desc_k_sw128(a_addr);
-          const uint64_t db = make_desc_k_sw128(a_addr + A_BYTES);
+          const uint64_t db = make_desc_k_sw128(a_addr + A_STAGE_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advancing 16 elements along K = 32 bytes = 2 descriptor units
-            if (CTAS == 2) {
+            if (SKINNY) {
+              // (Spreading the k-steps over several accumulators per half, so that consecutive MMAs
+              // do not add to the same columns, was measured and changed nothing: an MMA of 16
+              // columns takes about 110 cycles either way.)
+              const uint32_t acc_flag = (kb > sg.kb0 || k > 0) ? 1u : 0u;
+              const uint32_t idesc_s = make_idesc_bf16(128, p.a_rows);
+              umma_bf16(d_tmem, db + 2u * k, da + 2u * k, idesc_s, acc_flag);
+              umma_bf16(d_tmem + static_cast<uint32_t>(p.a_rows), db + (B_HALF_BYTES >> 4) + 2u * k, da + 2u * k, idesc_s,
+                        acc_flag);
+            } else if (CTAS == 2) {
               umma_bf16_2cta(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb > sg.kb0 || k > 0) ? 1u : 0u);
             } else {
               umma_bf16(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb > sg.kb0 || k > 0) ? 1u : 0u);
@@ -482,6 +516,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     // ---------------------------------------------------------- epilogue
     const int q = warp - 4;  // == warp % 4: the TMEM lane quarter this warp may read
     int it = 0;
+    int sk_pending = 0, sk_tile[2] = {0, 0}, sk_n0[2] = {0, 0};  // SKINNY stream-K: tiles this CTA delivered partial sums for
     SegmentIter segs(p, rows_tiles_m, rows_num_tiles, unit, num_units, FUSED);
     Segment sg;
     for (; segs.next<ROLE_EPILOGUE>(sg, ring, dl, lane); ++it) {
@@ -503,6 +538,67 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       const uint32_t t_acc = tmem_base + static_cast<uint32_t>(acc * ACC_COLS) + (static_cast<uint32_t>(q * 32) << 16);
       __nv_bfloat16* crow = c_base + static_cast<size_t>(row) * c_ld;
       const bool row_ok = row < rows_m && !(p.debug & 2);
+
+      if (SKINNY) {
+        // this thread owns weight row i of both halves: output column n0 + i (gate/up), or the
+        // columns n0 + i and n0 + 128 + i (plain); the accumulator columns are the rows of A
+        const int i = row_in_tile;
+        const int n_rows = p.a_rows;
+        const bool whole = p.sk_per == 0 || (sg.kb0 == 0 && sg.kb1 == p.num_kb);
+        // Stream-K: every segment that is not a whole tile delivers its partial sums, [row of A]
+        // [256] fp32 (the 128 D0 lanes, then the 128 D1 lanes), to one of this CTA's two slots --
+        // slot 0 for a segment that starts inside a tile, slot 1 for one that starts a tile. The
+        // tile is finished after the segment loop, by all of its contributors together.
+        float* mine = p.sk_partials + static_cast<size_t>(2 * unit + (sg.kb0 > 0 ? 0 : 1)) * (ACC_COLS * BM);
+        const int col0 = n0 + i;
+        const int col1 = (tmode == MODE_GATEUP) ? col0 : col0 + 128;
+#pragma unroll 1
+        for (int c = 0; c < n_rows / 16; ++c) {
+          uint32_t d0[16], d1[16];
+          tmem_ld_32x16(t_acc + c * 16, d0);
+          tmem_ld_32x16(t_acc + n_rows + c * 16, d1);
+          tmem_ld_wait();
+          if (!whole) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (c * 16 + j < rows_m) {
+                mine[(c * 16 + j) * ACC_COLS + i] = __uint_as_float(d0[j]);
+                mine[(c * 16 + j) * ACC_COLS + 128 + i] = __uint_as_float(d1[j]);
+              }
+            }
+            continue;
+          }
+          if (p.debug & 2) continue;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int r = c * 16 + j;
+            if (r < rows_m) {
+              __nv_bfloat16* dst = c_base + static_cast<size_t>(r) * c_ld;
+              if (tmode == MODE_GATEUP) {
+                const float g = round_bf16(__uint_as_float(d0[j]));
+                const float u = round_bf16(__uint_as_float(d1[j]));
+                if (col0 < c_cols) dst[col0] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * u);
+              } else {
+                if (col0 < c_cols) dst[col0] = __float2bfloat16_rn(__uint_as_float(d0[j]));
+                if (col1 < c_cols) dst[col1] = __float2bfloat16_rn(__uint_as_float(d1[j]));
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&tempty[acc]);
+        if (!whole) {
+          __threadfence();
+          epilogue_bar_sync();
+          if (threadIdx.x == 4 * 32) atomicAdd(p.sk_counters + t, 1u);
+          if (sk_pending < 2) {
+            sk_tile[sk_pending] = t;
+            sk_n0[sk_pending] = n0;
+          }
+          ++sk_pending;
+        }
+        continue;
+      }
 
       // ---- stream-K: a segment that does not start at k = 0 only delivers its fp32 partial
       // sums; the CTA that owns the tile's first k-blocks (it reaches them last) adds the
@@ -636,6 +732,103 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         mbar_arrive(&tempty[acc]);
       }
     }
+    if (SKINNY && sk_pending > 0 && !*abort_flag) {
+      // Finish the tiles this CTA holds partial sums of. Tile t was cut into S segments, held by
+      // the consecutive CTAs first..first+S-1 in k order; once all S have delivered, contributor s
+      // sums the s-th share of the tile's (row of A, weight row) pairs over the S partials -- in k
+      // order, so the result does not depend on timing -- and stores those outputs. Every CTA has
+      // delivered all its partial sums before it waits here, so the waits cannot form a cycle.
+      const int tid = static_cast<int>(threadIdx.x) - 4 * 32;
+      const int c_ld = p.ldc, c_cols = p.N;
+      for (int k = 0; k < (sk_pending < 2 ? sk_pending : 2); ++k) {
+        const int t = sk_tile[k];
+        const int first = static_cast<int>((static_cast<long long>(t) * p.num_kb) / p.sk_per);
+        const int last = static_cast<int>((static_cast<long long>(t + 1) * p.num_kb - 1) / p.sk_per);
+        const int S = last - first + 1;
+        const int s_idx = unit - first;
+        if (tid == 0) {
+          uint32_t spins = 0;
+          while (ld_acquire_gpu(p.sk_counters + t) < static_cast<unsigned>(S)) {
+            if ((++spins & 0xffu) == 0u) {
+              if (*dl.abort) break;
+              if (globaltimer_ns() > dl.t_end) {
+                *dl.abort = 1u;
+                report(dl.status, 1u, WHERE_SK_PARTIALS, static_cast<unsigned>(t));
+                break;
+              }
+            }
+          }
+        }
+        epilogue_bar_sync();
+        if (*dl.abort) break;
+        const int E = rows_m * 128;
+        const int lo = static_cast<int>(static_cast<long long>(s_idx) * E / S);
+        const int hi = static_cast<int>(static_cast<long long>(s_idx + 1) * E / S);
+        const float* base = p.sk_partials + static_cast<size_t>(2 * first) * (ACC_COLS * BM);
+        // four pairs per pass and four contributors per batch: 32 loads in flight per thread
+        for (int e0 = lo + tid; e0 < hi; e0 += 4 * 128) {
+          const float* src[4];
+          float a0[4], a1[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int e = min(e0 + u * 128, hi - 1);  // a clamped pair is summed again and not stored
+            src[u] = base + (e >> 7) * ACC_COLS + (e & 127);
+            // contributor 0 started the tile (slot 1); the others started inside it (slot 0)
+            a0[u] = __ldcg(src[u] + ACC_COLS * BM);
+            a1[u] = __ldcg(src[u] + ACC_COLS * BM + 128);
+          }
+          int o = 1;
+          for (; o + 4 <= S; o += 4) {
+            float v0[4][4], v1[4][4];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                v0[w][u] = __ldcg(src[u] + static_cast<size_t>(o + w) * (2 * ACC_COLS * BM));
+                v1[w][u] = __ldcg(src[u] + static_cast<size_t>(o + w) * (2 * ACC_COLS * BM) + 128);
+              }
+            }
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+#pragma unroll
+              for (int u = 0; u < 4; ++u) {
+                a0[u] += v0[w][u];
+                a1[u] += v1[w][u];
+              }
+            }
+          }
+          for (; o < S; ++o) {
+            float v0[4], v1[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              v0[u] = __ldcg(src[u] + static_cast<size_t>(o) * (2 * ACC_COLS * BM));
+              v1[u] = __ldcg(src[u] + static_cast<size_t>(o) * (2 * ACC_COLS * BM) + 128);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              a0[u] += v0[u];
+              a1[u] += v1[u];
+            }
+          }
+          if (p.debug & 2) continue;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int e = e0 + u * 128;
+            if (e >= hi) break;
+            __nv_bfloat16* dst = p.C + static_cast<size_t>(e >> 7) * c_ld;
+            const int col0 = sk_n0[k] + (e & 127);
+            if (MODE == MODE_GATEUP) {
+              const float g = round_bf16(a0[u]);
+              const float up = round_bf16(a1[u]);
+              if (col0 < c_cols) dst[col0] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * up);
+            } else {
+              if (col0 < c_cols) dst[col0] = __float2bfloat16_rn(a0[u]);
+              if (col0 + 128 < c_cols) dst[col0 + 128] = __float2bfloat16_rn(a1[u]);
+            }
+          }
+        }
+      }
+    }
   }
 
   // ------------------------------------------------------------ teardown
@@ -724,7 +917,7 @@ static int max_active_pairs() {
 }
 
 constexpr size_t kSkCounterBytes = 8192;                      // up to 2048 tiles
-constexpr size_t kSkPartialBytes = size_t(ACC_COLS) * BM * 4;  // one 128 x 256 fp32 tile per CTA
+constexpr size_t kSkPartialBytes = 2 * size_t(ACC_COLS) * BM * 4;  // two 128 x 256 fp32 tiles per CTA
 
 static size_t splitk_workspace_bytes_for(int sms) {
   return kSkCounterBytes + static_cast<size_t>(sms) * kSkPartialBytes;
@@ -732,13 +925,19 @@ static size_t splitk_workspace_bytes_for(int sms) {
 
 template <int MODE, int CTAS>
 static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b0, const CUtensorMap& tm_b1, GemmParams p,
-                          int max_ctas, int sms, void* sk_ws, size_t sk_ws_bytes, cudaStream_t stream) {
+                          int max_ctas, int sms, void* sk_ws, size_t sk_ws_bytes, cudaStream_t stream,
+                          bool skinny = false) {
   using Cfg = TileCfg<CTAS>;
   constexpr int BN_OUT = (MODE == MODE_GATEUP) ? 128 : 256;
   static_assert(MODE != MODE_FUSED, "the fused launch has its own host path");
   // the attribute is per device; setting it on every call is cheap and covers every device that launches
-  const cudaError_t attr_err =
-      cudaFuncSetAttribute(gemm_tc_kernel<MODE, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  const int smem_bytes = (CTAS == 2) ? Cfg::kSmemBytes : p.stages * stage_bytes_for(p.a_rows) + 1024 + 512;
+  auto kernel = gemm_tc_kernel<MODE, CTAS, false>;
+  if constexpr (CTAS == 1) {
+    if (skinny) kernel = gemm_tc_kernel<MODE, 1, true>;
+  }
+  const cudaError_t attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                    (CTAS == 2) ? Cfg::kSmemBytes : kMaxSmemBytes);
   if (attr_err != cudaSuccess) return fail(DF_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(attr_err));
 
   p.tiles_m = (p.M + Cfg::kTileM - 1) / Cfg::kTileM;
@@ -760,7 +959,9 @@ static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b0, con
     const int waves = (p.num_tiles + units - 1) / units;
     const double eff = static_cast<double>(p.num_tiles) / (static_cast<double>(waves) * units);
     const long long total = static_cast<long long>(p.num_tiles) * p.num_kb;
-    if (eff < 0.6 && p.num_tiles <= units && p.num_kb >= 8 &&
+    // a launch that streams the weights once (few rows) is bound by the bytes in flight: every SM counts
+    const double eff_min = 0.01 * tuning_int(skinny ? "DF_GEMM_SK_EFF_SKINNY" : "DF_GEMM_SK_EFF", 60);
+    if (eff < eff_min && p.num_tiles <= units && p.num_kb >= 8 &&
         static_cast<size_t>(p.num_tiles) * 4 <= kSkCounterBytes - 64) {
       long long g = units;
       if (g > total / 4) g = total / 4;  // at least four k-blocks per CTA
@@ -788,13 +989,13 @@ static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b0, con
   }
 
   if (tuning_int("DF_DEBUG", 0) > 0)
-    std::fprintf(stderr, "[df] gemm mode=%d ctas=%d M=%d N=%d K=%d tiles=%d grid=%d group_m=%d streamk_per=%d\n", MODE,
-                 CTAS, p.M, p.N, p.K, p.num_tiles, units * CTAS, p.group_m, p.sk_per);
+    std::fprintf(stderr, "[df] gemm mode=%d ctas=%d M=%d N=%d K=%d tiles=%d grid=%d group_m=%d streamk_per=%d a_rows=%d stages=%d skinny=%d\n",
+                 MODE, CTAS, p.M, p.N, p.K, p.num_tiles, units * CTAS, p.group_m, p.sk_per, p.a_rows, p.stages, int(skinny));
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(units * CTAS, 1, 1);
   cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr;
   attr.id = cudaLaunchAttributeClusterDimension;
@@ -803,7 +1004,7 @@ static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b0, con
   attr.val.clusterDim.z = 1;
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<MODE, CTAS>, tm_a, tm_b0, tm_b1, tm_a, tm_b0, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b0, tm_b1, tm_a, tm_b0, p);
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
     return fail(DF_ECUDA, "gemm launch (%d-CTA tiles): %s", CTAS, cudaGetErrorString(e));
@@ -824,10 +1025,10 @@ static int launch_fused_mlp(const void* x, const void* wg, const void* wu, void*
                                                     cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   if (attr_err != cudaSuccess) return fail(DF_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(attr_err));
   CUtensorMap tm_x, tm_g, tm_u, tm_h, tm_d;
-  if (!make_map_bf16(&tm_x, x, M, H, H, BM)) return DF_ECUDA;
+  if (!make_map_bf16(&tm_x, x, M, H, H, M < BM ? M : BM)) return DF_ECUDA;
   if (!make_map_bf16(&tm_g, wg, I, H, H, 128)) return DF_ECUDA;
   if (!make_map_bf16(&tm_u, wu, I, H, H, 128)) return DF_ECUDA;
-  if (!make_map_bf16(&tm_h, h, M, I, I, BM)) return DF_ECUDA;
+  if (!make_map_bf16(&tm_h, h, M, I, I, M < BM ? M : BM)) return DF_ECUDA;
   if (!make_map_bf16(&tm_d, wd, H, I, I, 128)) return DF_ECUDA;
 
   GemmParams p;
@@ -849,6 +1050,9 @@ static int launch_fused_mlp(const void* x, const void* wg, const void* wu, void*
   p.timeout_ns = timeout_ns();
   p.status = reinterpret_cast<Status*>(dev_status);
   p.debug = tuning_int("DF_GEMM_DEBUG", 0);
+  p.a_rows = BM;
+  p.a_tx = (M < BM ? M : BM) * BK * 2;
+  p.stages = Cfg::kStages;
   int g = tuning_int("DF_GEMM_GROUP_M", 32);
   if (g < 1) g = 1;
   while (2 * ((p.tiles_m + g - 1) / g) > kMaxChunks) g *= 2;
@@ -919,8 +1123,13 @@ static int launch_gemm(const void* a, const void* b0, const void* b1, void* c, i
   int sms = df_sm_count();
   if (sms <= 0) return fail(DF_ECUDA, "no CUDA device");
 
+  // At most 64 rows: the operand-swapped form with a smaller A stage and a deeper pipeline.
+  const bool skinny = M <= tuning_int("DF_GEMM_SKINNY_ROWS", 128) && M <= BM && m_dev == nullptr && tuning_int("DF_GEMM_SKINNY", 1) != 0 &&
+                      tuning_int("DF_GEMM_CTAS", 1) != 2;
+  const int a_rows = skinny ? ((M + 15) / 16) * 16 : BM;
+  const int a_box_rows = M < BM ? M : BM;  // a launch of fewer than 128 rows never copies past its last row
   CUtensorMap tm_a, tm_b0, tm_b1;
-  if (!make_map_bf16(&tm_a, a, M, K, lda, BM)) return DF_ECUDA;
+  if (!make_map_bf16(&tm_a, a, M, K, lda, a_box_rows)) return DF_ECUDA;
   if (!make_map_bf16(&tm_b0, b0, N, K, ldb, 128)) return DF_ECUDA;
   if (!make_map_bf16(&tm_b1, b1, N, K, ldb, 128)) return DF_ECUDA;
 
@@ -940,6 +1149,11 @@ static int launch_gemm(const void* a, const void* b0, const void* b1, void* c, i
   p.tile_counter = nullptr;
   p.m_dev = m_dev;
   p.debug = tuning_int("DF_GEMM_DEBUG", 0);
+  p.a_rows = a_rows;
+  p.a_tx = a_box_rows * BK * 2;
+  p.stages = skinny ? stages_for(a_rows) : TileCfg<1>::kStages;
+  const int stage_cap = tuning_int("DF_GEMM_STAGES", 0);  // development only: a shallower pipeline
+  if (stage_cap >= 2 && stage_cap < p.stages) p.stages = stage_cap;
 
   // One CTA per tile is the default: measured on B200 under the power cap, the CTA-pair
   // variant moves a third less data from L2 but keeps the tensor pipe slightly less busy
@@ -950,7 +1164,7 @@ static int launch_gemm(const void* a, const void* b0, const void* b1, void* c, i
   if (two)
     return launch_variant<MODE, 2>(tm_a, tm_b0, tm_b1, p, max_ctas, sms, nullptr, 0, static_cast<cudaStream_t>(stream));
   return launch_variant<MODE, 1>(tm_a, tm_b0, tm_b1, p, max_ctas, sms, sk_ws, sk_ws_bytes,
-                                 static_cast<cudaStream_t>(stream));
+                                 static_cast<cudaStream_t>(stream), skinny);
 }
 
 }  // namespace df
