@@ -174,6 +174,25 @@ def workload_config(n_gpus: int) -> dict:
             "parallelism": f"tp{n_gpus}", "l2": "inputs larger than L2 (weights 352 MB + activations 604 MB per step)"}
 
 
+def comm_plan(args, world: int) -> dict:
+    """How the reduction and the GEMMs share the GPU at N > 1 (flags override the defaults): the
+    reduction inside the NVLink switch on 16 CTAs, on 8 SMs that the GEMMs leave free."""
+    if world == 1:
+        return {"comm": None, "comm_ctas": 0, "gemm_ctas": 0, "exclusive_sms": False}
+    import torch
+
+    kind = args.comm
+    if kind == "auto":
+        from dynaflow_b200.comm import multicast_supported
+
+        kind = "multicast" if multicast_supported() else "peer"
+    comm_ctas = args.comm_ctas if args.comm_ctas > 0 else (16 if kind == "multicast" else 32)
+    exclusive = not args.shared_sms
+    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    gemm_ctas = args.gemm_ctas if args.gemm_ctas >= 0 else (sms - (comm_ctas + 1) // 2 if exclusive else 0)
+    return {"comm": kind, "comm_ctas": comm_ctas, "gemm_ctas": gemm_ctas, "exclusive_sms": exclusive}
+
+
 # ------------------------------------------------------------------ GPU arm
 def run_ours(args) -> None:
     import torch
@@ -193,12 +212,16 @@ def run_ours(args) -> None:
         dist.init_process_group("nccl", device_id=dev)
 
     comm = None
+    plan = comm_plan(args, world)
     if world > 1:
-        from dynaflow_b200.comm import PeerComm
+        from dynaflow_b200.comm import MulticastComm, PeerComm, set_exclusive_sms
 
-        comm = PeerComm(rank, world, ROWS // MICRO_BATCHES, H, slots=MICRO_BATCHES, n_ctas=args.comm_ctas, device=dev)
+        comm_cls = MulticastComm if plan["comm"] == "multicast" else PeerComm
+        comm = comm_cls(rank, world, ROWS // MICRO_BATCHES, H, slots=MICRO_BATCHES, n_ctas=plan["comm_ctas"], device=dev)
+        set_exclusive_sms(plan["exclusive_sms"])
     layer = TensorParallelGatedMLP(H, I, rank=rank, world=world, max_rows=ROWS // MICRO_BATCHES,
                                    micro_batches=MICRO_BATCHES, seed=0, device=dev, comm=comm)
+    layer.gemm_max_ctas = plan["gemm_ctas"]
     gen = torch.Generator().manual_seed(1)
     x_host = torch.randn(ROWS, H, generator=gen).bfloat16().pin_memory()
     out_host = torch.empty(ROWS, H, dtype=torch.bfloat16).pin_memory()
@@ -221,15 +244,19 @@ def run_ours(args) -> None:
     sampler = ClockSampler(local_rank) if rank == 0 else None
 
     # ---- device-resident: value, and per-kernel times for the roofline
+    # Consecutive steps pipeline like consecutive layers: the reduction of a step's last micro-batch
+    # runs under the next step's first GEMMs; the stream joins the reductions before the end mark.
     for _ in range(args.warmup):
-        layer.forward_device(x_dev, out_dev, cuts)
+        layer.forward_device(x_dev, out_dev, cuts, join=False)
+    layer.wait_reductions()
     barrier()
     marks = []
     t_wall0 = time.time()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
     for _ in range(args.steps):
-        marks.append(layer.forward_device(x_dev, out_dev, cuts, record_kernel_events=True))
+        marks.append(layer.forward_device(x_dev, out_dev, cuts, record_kernel_events=True, join=False))
+    layer.wait_reductions()
     end.record()
     barrier()
     t_wall1 = time.time()
@@ -296,9 +323,14 @@ def run_ours(args) -> None:
     if sampler is not None:
         sampler.stop()
 
+    comm_summary = layer.comm_summary()
+    if world > 1:
+        # every rank leaves together: the regions are unmapped only once nobody can touch them any more
+        barrier()
+        comm.close()
+        dist.barrier()
+        dist.destroy_process_group()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
         return
 
     peaks, peak_kind = measured_peaks()
@@ -328,7 +360,8 @@ def run_ours(args) -> None:
     line = {
         "metric": METRIC, "value": ROWS / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": dict(workload_config(world), **({"reduction": plan} if world > 1 else {})),
         "e2e": {"value": ROWS / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": ROWS * H * 2, "d2h_bytes_per_step": ROWS * H * 2},
         "gpu_launches": layer.launches_per_step * args.steps,
@@ -345,8 +378,7 @@ def run_ours(args) -> None:
         "sweep": sweep,
     }
     if world > 1:
-        line["comm"] = dict(layer.comm_summary(), **(comm_stats or {}))
-        dist.destroy_process_group()
+        line["comm"] = dict(comm_summary, **(comm_stats or {}))
     print(json.dumps(line))
 
 
@@ -425,8 +457,14 @@ def run_decoder(args) -> None:
         dist.init_process_group("nccl", device_id=dev)
     shape = DecoderShape(layers=args.layers)
     batch, seq = 8, 2048
+    plan = comm_plan(args, world)
+    if world > 1:
+        from dynaflow_b200.comm import set_exclusive_sms
+
+        set_exclusive_sms(plan["exclusive_sms"])
     dec = TensorParallelDecoder(shape, rank=rank, world=world, max_rows=batch * seq // MICRO_BATCHES,
-                                micro_batches=MICRO_BATCHES, seed=0, device=dev, n_ctas=args.comm_ctas)
+                                micro_batches=MICRO_BATCHES, seed=0, device=dev, n_ctas=plan["comm_ctas"],
+                                multicast=plan["comm"] == "multicast", gemm_max_ctas=plan["gemm_ctas"])
     ids = torch.randint(0, shape.vocab, (batch, seq), generator=torch.Generator().manual_seed(1)).to(dev)
 
     def timed(**kw):
@@ -453,7 +491,7 @@ def run_decoder(args) -> None:
     ops.check_status()
     line = {"workload": f"Llama-3-8B-shaped decoder prefill, {shape.layers} layers, ids {batch}x{seq}, "
                         f"{MICRO_BATCHES} micro-batches, tp{world}",
-            "metric": "prefill tokens/sec", "unit": "tokens/s", "n_gpus": world, "ms_per_forward": t_all,
+            "metric": "prefill tokens/sec", "unit": "tokens/s", "n_gpus": world, "ms_per_forward": t_all, "reduction": plan,
             "value": batch * seq / (t_all * 1e-3)}
     peaks, kind = measured_peaks()
     s = shape
@@ -477,8 +515,12 @@ def run_decoder(args) -> None:
         line["frac_of_roofline"] = line["comm"]["roofline_ms"] / t_all
     if rank == 0:
         print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
     dec.close()
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 
@@ -491,7 +533,15 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--rows", type=int, default=ROWS, help="rows per step (default: the benchmark's 16384; "
                     "smaller values are for profiler captures only)")
-    ap.add_argument("--comm-ctas", type=int, default=32, help="CTAs of the peer-memory all-reduce kernel (N > 1)")
+    ap.add_argument("--comm", choices=["auto", "multicast", "peer"], default="auto",
+                    help="N > 1: reduction inside the NVLink switch (multimem kernel) or over peer memory (two-shot "
+                         "kernel); auto = multicast where the devices offer it")
+    ap.add_argument("--comm-ctas", type=int, default=0, help="CTAs of the reduction kernel (N > 1; 0 = 16 for multicast, "
+                    "32 for peer)")
+    ap.add_argument("--gemm-ctas", type=int, default=-1, help="CTAs the GEMMs may use at N > 1 (0 = one per SM; default: "
+                    "the SMs minus the ones the reduction's CTAs fill, two per SM)")
+    ap.add_argument("--shared-sms", action="store_true", help="N > 1: let reduction CTAs share SMs with GEMM CTAs instead "
+                    "of running on SMs of their own")
     ap.add_argument("--replicated-residual", action="store_true",
                     help="N > 1 chain: keep the residual stream replicated on every rank instead of sharded by rows")
     ap.add_argument("--workload", choices=["mlp", "decoder"], default="mlp",

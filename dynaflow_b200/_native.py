@@ -68,6 +68,8 @@ SIGNATURES: dict[str, tuple] = {
     "df_rope_bf16": (_i, [_vp, _vp, _i, _i, _i, _i, _f, _vp]),
     "df_allreduce_add_rmsnorm_bf16": (_i, [_rank_p, _i, _i, _i, _i, _vp, _f, _i, _vp, _vp]),
     "df_allreduce_add_rmsnorm_sharded_bf16": (_i, [_rank_p, _i, _i, _i, _i, _vp, _f, _i, _vp, _vp]),
+    "df_comm_set_exclusive_smem": (_i, [_i]),
+    "df_allreduce_multicast_bf16": (_i, [_rank_p, _vp, _i, _i, _i, _i, _i, _vp, _f, _i, _vp, _vp]),
     "df_add_rmsnorm_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _i, _i, _vp]),
     "df_allreduce_emulated_bf16": (_i, [_rank_p, _i, _i, _i, _i, _vp, _f, _i, _i, _vp, _vp]),
     "df_mlp_gated_bf16_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),

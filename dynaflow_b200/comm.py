@@ -3,8 +3,12 @@
 ``PeerComm`` is the multi-process form (one process per GPU): every rank allocates
 one region per micro-batch slot through the C ABI, the 64-byte CUDA IPC handles are
 exchanged with ``torch.distributed.all_gather_object`` (plumbing only), and each
-rank maps its peers' regions. ``EmulatedComm`` keeps all ranks' regions on one GPU
-and runs them as one cooperative launch (tests without a second GPU).
+rank maps its peers' regions. ``MulticastComm`` is the same communicator over an
+NVLink multicast mapping (the regions come from ``torch.distributed._symmetric_memory``,
+again plumbing only): the all-reduce and the sharded-residual fused form then reduce
+inside the switch (``multimem.ld_reduce`` / ``multimem.st`` in the library's own
+kernel). ``EmulatedComm`` keeps all ranks' regions on one GPU and runs them as one
+cooperative launch (tests without a second GPU).
 
 The all-reduce replaces the ``network``-tagged all-reduce (+ RMSNorm) subgraph of a
 TP model (``examples/ae/scheduler/vllm/nanoflow.py:59-69, 171-211``); a policy
@@ -38,6 +42,27 @@ def _bf16_view(ptr: int, rows: int, hidden: int, device: torch.device) -> torch.
 def _check(rc: int, what: str) -> None:
     if rc != 0:
         raise RuntimeError(f"{what} failed ({rc}): {_native.last_error()}")
+
+
+def set_exclusive_sms(on: bool) -> None:
+    """Process-wide: with ``True`` every reduction CTA claims 40 KB of shared memory it does not
+    use, which keeps it off the SMs that hold a GEMM CTA (and GEMM CTAs off its SM). Together with
+    GEMMs launched on fewer CTAs than SMs (``TensorParallelGatedMLP.gemm_max_ctas``) the reduction
+    then runs on SMs of its own, two CTAs per free SM."""
+    _check(_native.load().df_comm_set_exclusive_smem(40960 if on else 0), "df_comm_set_exclusive_smem")
+
+
+def multicast_supported(device: int | None = None) -> bool:
+    """Whether the current (or given) device offers NVLink multicast mappings (driver attribute
+    CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED)."""
+    try:
+        from cuda.bindings import driver as cu
+    except ImportError:                      # older cuda-python layout
+        from cuda import cuda as cu
+    dev = torch.cuda.current_device() if device is None else device
+    torch.cuda.init()
+    err, value = cu.cuDeviceGetAttribute(cu.CUdevice_attribute.CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED, dev)
+    return int(err) == 0 and int(value) == 1
 
 
 class _Regions:
@@ -78,6 +103,24 @@ class PeerComm(_Regions):
         super().__init__(world, max_rows, hidden, slots, n_ctas, device)
         self.rank = rank
         self.local: list[int] = []
+        self._opened: list[int] = []
+        self.regions: list[list[int]] = []
+        self._map_regions(group)
+        if world > 1:
+            dist.barrier(group=group)  # every rank has mapped every region before anyone launches
+        self._partials = [_bf16_view(self.local[s] + self.partial_off, max_rows, hidden, device) for s in range(slots)]
+        self._sums = [_bf16_view(self.local[s] + self.sum_off, max_rows, hidden, device) for s in range(slots)]
+        self.stream = torch.cuda.Stream(device=device)
+        # per-slot argument blocks of the plain all-reduce, built once (the launch path stays short)
+        self._plain_views = [self._view(rank, self.regions[s]) for s in range(slots)]
+        self._status_ptr = ops.status_block(device).data_ptr()
+
+    def _map_regions(self, group: Any) -> None:
+        """Fills ``self.local[slot]`` and ``self.regions[slot][r]`` (rank r's region of that slot as
+        mapped in this process): allocation through the C ABI, CUDA IPC handles for the peers."""
+        import torch.distributed as dist
+
+        world, rank, slots, device = self.world, self.rank, self.slots, self.device
         handles: list[bytes] = []
         with torch.cuda.device(device):
             for _ in range(slots):
@@ -92,9 +135,6 @@ class PeerComm(_Regions):
             dist.all_gather_object(gathered, handles, group=group)
         else:
             gathered[0] = handles
-        # regions[slot][r] = rank r's region for that slot, as mapped in this process
-        self.regions: list[list[int]] = []
-        self._opened: list[int] = []
         with torch.cuda.device(device):
             for slot in range(slots):
                 row = []
@@ -108,14 +148,6 @@ class PeerComm(_Regions):
                     row.append(ptr.value)
                     self._opened.append(ptr.value)
                 self.regions.append(row)
-        if world > 1:
-            dist.barrier(group=group)  # every rank has mapped every region before anyone launches
-        self._partials = [_bf16_view(self.local[s] + self.partial_off, max_rows, hidden, device) for s in range(slots)]
-        self._sums = [_bf16_view(self.local[s] + self.sum_off, max_rows, hidden, device) for s in range(slots)]
-        self.stream = torch.cuda.Stream(device=device)
-        # per-slot argument blocks of the plain all-reduce, built once (the launch path stays short)
-        self._plain_views = [self._view(rank, self.regions[s]) for s in range(slots)]
-        self._status_ptr = ops.status_block(device).data_ptr()
 
     def partial(self, slot: int, rows: int) -> torch.Tensor:
         """Where this rank's partial sums of micro-batch slot ``slot`` must be written."""
@@ -190,6 +222,67 @@ class PeerComm(_Regions):
             for ptr in self.local:
                 self.lib.df_comm_region_free(ptr)
         self._opened, self.local = [], []
+
+
+class MulticastComm(PeerComm):
+    """``PeerComm`` whose regions are bound to an NVLink multicast object, so that the all-reduce
+    and the sharded-residual fused form reduce inside the switch (``df_allreduce_multicast_bf16``).
+    The regions are one ``torch.distributed._symmetric_memory`` allocation per rank, which also
+    provides every peer's mapping (the flag barriers and the replicated-residual form keep using
+    those). Raises if the devices offer no multicast mapping. All ranks must leave together: a
+    rank that dies while its memory is bound to the multicast object can fault its peers' GPUs."""
+
+    def _map_regions(self, group: Any) -> None:
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        pg = group if group is not None else dist.group.WORLD
+        stride = (self.region_bytes + 4095) // 4096 * 4096
+        self._symm = symm.empty(stride * self.slots, dtype=torch.uint8, device=self.device)
+        self._symm.zero_()                    # flag words and sequence numbers start at zero
+        torch.cuda.synchronize(self.device)
+        self._handle = symm.rendezvous(self._symm, pg.group_name)
+        mc = int(getattr(self._handle, "multicast_ptr", 0) or 0)
+        if mc == 0:
+            raise RuntimeError("these devices expose no NVLink multicast mapping; use PeerComm")
+        ptrs = [int(p) for p in self._handle.buffer_ptrs]
+        self.local = [ptrs[self.rank] + s * stride for s in range(self.slots)]
+        self.regions = [[ptrs[r] + s * stride for r in range(self.world)] for s in range(self.slots)]
+        self.multicast = [mc + s * stride for s in range(self.slots)]
+
+    def all_reduce(self, slot: int, rows: int) -> torch.Tensor:
+        rc = self.lib.df_allreduce_multicast_bf16(ctypes.byref(self._plain_views[slot]), self.multicast[slot], self.world,
+                                                  self.max_rows, self.hidden, rows, 0, None, 0.0, self.n_ctas,
+                                                  self._status_ptr, torch.cuda.current_stream(self.device).cuda_stream)
+        if rc != 0:
+            _check(rc, "df_allreduce_multicast_bf16")
+        self.launches += 1
+        self.bytes_reduced += rows * self.hidden * 2
+        return self._sums[slot][:rows]
+
+    def all_reduce_add_rmsnorm_sharded(self, slot: int, rows: int, residual: torch.Tensor, weight: torch.Tensor,
+                                       eps: float = 1e-5, first: bool = False) -> torch.Tensor:
+        view = self._view(self.rank, self.regions[slot], None if first else residual, residual, None)
+        rc = self.lib.df_allreduce_multicast_bf16(ctypes.byref(view), self.multicast[slot], self.world, self.max_rows,
+                                                  self.hidden, rows, 1, weight.data_ptr(), eps, self.n_ctas,
+                                                  self._status_ptr, torch.cuda.current_stream(self.device).cuda_stream)
+        if rc != 0:
+            _check(rc, "df_allreduce_multicast_bf16")
+        self.launches += 1
+        self.bytes_reduced += rows * self.hidden * 2
+        return self._sums[slot][:rows]
+
+    def summary(self) -> dict:
+        return {"kind": "in-switch all-reduce over an NVLink multicast mapping (hand-written multimem kernel, "
+                        "no NCCL on the data path)",
+                "n_ctas": self.n_ctas, "launches": self.launches, "payload_bytes": self.bytes_reduced}
+
+    def close(self) -> None:
+        torch.cuda.synchronize(self.device)
+        self._partials, self._sums = [], []
+        self.local, self.regions, self.multicast = [], [], []
+        self._handle = None
+        self._symm = None
 
 
 def add_rmsnorm(y: torch.Tensor, residual: torch.Tensor | None, weight: torch.Tensor, out: torch.Tensor,

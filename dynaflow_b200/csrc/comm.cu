@@ -361,6 +361,123 @@ __global__ void __launch_bounds__(kCommThreads, 2) allreduce_kernel(const CommPa
   if (threadIdx.x == 0) me.seq[blockIdx.x] = seq + 1u;  // also after a failed wait: the ranks stay in step
 }
 
+// ---------------------------------------------------- in-switch (multicast) form
+// The same two shots over an NVLink multicast mapping of the ranks' regions: one
+// multimem.ld_reduce returns a 16-byte vector already summed over all ranks by the switch (fp32
+// accumulation, rounded to bf16 once), one multimem.st delivers a vector to every rank. Per
+// output vector that is one load and one store instead of `world` of each, and for a message
+// of S bytes S bytes cross a GPU's links in each direction instead of 2 (W-1)/W * S.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_bf16x8(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+template <int EPI>  // EPI_NONE or EPI_ADD_RMSNORM_SHARDED
+__global__ void __launch_bounds__(kCommThreads, 2)
+allreduce_multicast_kernel(const CommParams p, const __nv_bfloat16* mc_partial, __nv_bfloat16* mc_sum) {
+  __shared__ uint32_t s_abort;
+  extern __shared__ uint4 s_weight[];
+  const RankView& me = p.ranks[0];
+  const int W = p.world;
+  if (threadIdx.x == 0) s_abort = 0u;
+  if (EPI != EPI_NONE && p.H <= kMaxSmemHidden) {
+    for (int v = threadIdx.x; v < (p.H >> 3); v += blockDim.x) s_weight[v] = reinterpret_cast<const uint4*>(p.weight)[v];
+  }
+  const unsigned long long t_end = globaltimer_ns() + p.timeout_ns;
+  const uint32_t seq = me.seq[blockIdx.x];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = p.H >> 3;
+  const int row_stride = gridDim.x * kWarpsPerBlock;
+  const int row_first = blockIdx.x * kWarpsPerBlock + warp;
+
+  // every rank's partial rows are complete and visible before the switch reads them
+  bool ok = peer_barrier(me, W, 0, seq, t_end, p.status, &s_abort);
+  if (ok) {
+    const int lo = static_cast<int>(static_cast<long long>(p.T) * me.rank / W);
+    const int hi = static_cast<int>(static_cast<long long>(p.T) * (me.rank + 1) / W);
+    constexpr int U = (EPI == EPI_NONE) ? 16 : 8;  // vectors in flight per lane
+    const uint4* wv1 = (p.H <= kMaxSmemHidden) ? s_weight : reinterpret_cast<const uint4*>(p.weight);
+    for (int row = lo + row_first; row < hi; row += row_stride) {
+      const size_t base = static_cast<size_t>(row) * p.H;
+      float ss = 0.0f;
+      for (int v0 = lane; v0 < nvec; v0 += 32 * U) {
+        uint4 in[U];
+        uint4 rs[(EPI == EPI_ADD_RMSNORM_SHARDED) ? U : 1];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int v = v0 + 32 * u;
+          if (v < nvec) {
+            in[u] = multimem_ld_reduce_bf16x8(reinterpret_cast<const uint4*>(mc_partial + base) + v);
+            if (EPI == EPI_ADD_RMSNORM_SHARDED)
+              rs[u] = me.residual_in != nullptr ? reinterpret_cast<const uint4*>(me.residual_in + base)[v]
+                                                : make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int v = v0 + 32 * u;
+          if (v < nvec) {
+            if (EPI == EPI_ADD_RMSNORM_SHARDED) {
+              float fy[8], fr[8];
+              unpack8(in[u], fy);
+              unpack8(rs[(EPI == EPI_ADD_RMSNORM_SHARDED) ? u : 0], fr);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) fy[i] += fr[i];
+              const uint4 packed = pack8(fy);
+              reinterpret_cast<uint4*>(me.residual_out + base)[v] = packed;
+              unpack8(packed, fy);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) ss += fy[i] * fy[i];
+            } else {
+              multimem_st_bf16x8(reinterpret_cast<uint4*>(mc_sum + base) + v, in[u]);
+            }
+          }
+        }
+      }
+      if (EPI == EPI_ADD_RMSNORM_SHARDED) {
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        const float inv = rsqrtf(ss / static_cast<float>(p.H) + p.eps);
+        const uint4* rnew = reinterpret_cast<const uint4*>(me.residual_out + base);
+        constexpr int kBatch = 8;
+        for (int v0 = lane; v0 < nvec; v0 += 32 * kBatch) {
+          uint4 xv[kBatch];
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u) {
+            const int v = v0 + 32 * u;
+            if (v < nvec) xv[u] = rnew[v];  // this thread's own writes
+          }
+#pragma unroll
+          for (int u = 0; u < kBatch; ++u) {
+            const int v = v0 + 32 * u;
+            if (v < nvec) {
+              float fx[8], fw[8];
+              unpack8(xv[u], fx);
+              unpack8(wv1[v], fw);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) fx[i] = __bfloat162float(__float2bfloat16_rn(fx[i] * inv)) * fw[i];
+              multimem_st_bf16x8(reinterpret_cast<uint4*>(mc_sum + base) + v, pack8(fx));
+            }
+          }
+        }
+      }
+    }
+    // every rank's slice has landed everywhere before anyone reads the result
+    ok = peer_barrier(me, W, 1, seq, t_end, p.status, &s_abort);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) me.seq[blockIdx.x] = seq + 1u;
+}
+
 // ------------------------------------------------------------------- host
 
 struct RegionLayout {
@@ -375,6 +492,12 @@ static RegionLayout region_layout(int max_rows, int hidden) {
   l.total = l.sum_off + buf;
   return l;
 }
+
+// Shared memory a reduction CTA claims beyond what it uses (0 = none). 40 KB keeps such a CTA off
+// every SM that holds a GEMM CTA (197 KB of the SM's 227 KB) and a GEMM CTA off every SM that
+// holds one: when the GEMMs are launched on fewer CTAs than there are SMs, the reduction then
+// runs on the SMs they leave free instead of sharing SMs with them.
+static int g_exclusive_smem = 0;
 
 template <bool EMULATE>
 static int launch_allreduce(const CommParams& p, int n_ctas, int emulated, void* stream) {
@@ -397,7 +520,12 @@ static int launch_allreduce(const CommParams& p, int n_ctas, int emulated, void*
       return fail(DF_EUNSUPPORTED, "world size %d is outside [1, %d]", p.world, kMaxWorld);
   }
   cudaError_t e;
-  const size_t smem = (p.mode != EPI_NONE && p.H <= kMaxSmemHidden) ? static_cast<size_t>(p.H) * 2 : 0;
+  size_t smem = (p.mode != EPI_NONE && p.H <= kMaxSmemHidden) ? static_cast<size_t>(p.H) * 2 : 0;
+  if (!EMULATE && g_exclusive_smem > 0) {
+    smem += static_cast<size_t>(g_exclusive_smem);
+    e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return fail(DF_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  }
   if (EMULATE) {
     // every emulated rank must be resident at once: its blocks wait on the others'
     e = cudaLaunchCooperativeKernel(fn, grid, block, args, smem, static_cast<cudaStream_t>(stream));
@@ -572,6 +700,48 @@ int df_allreduce_add_rmsnorm_sharded_bf16(const df_comm_rank_t* view, int world,
                           dev_status);
   if (r != DF_OK) return r;
   return df::launch_allreduce<false>(p, df::clamp_ctas(n_ctas), 1, stream);
+}
+
+int df_comm_set_exclusive_smem(int bytes) {
+  if (bytes < 0 || bytes > 96 * 1024) return df::fail(DF_EINVAL, "exclusive shared memory must be within [0, 98304] bytes");
+  df::g_exclusive_smem = bytes;
+  return DF_OK;
+}
+
+int df_allreduce_multicast_bf16(const df_comm_rank_t* view, void* mc_region, int world, int max_rows, int hidden, int T,
+                                int fuse, const void* weight, float eps, int n_ctas, df_status_t* dev_status,
+                                void* stream) {
+  if (mc_region == nullptr || (reinterpret_cast<uintptr_t>(mc_region) & 255u) != 0)
+    return df::fail(DF_EINVAL, "the multicast address of the region is NULL or not 256-byte aligned");
+  if (fuse != 0 && fuse != 1) return df::fail(DF_EINVAL, "fuse must be 0 (all-reduce) or 1 (sharded add + RMSNorm)");
+  df::CommParams p;
+  const int mode = fuse ? df::EPI_ADD_RMSNORM_SHARDED : df::EPI_NONE;
+  int r = df::fill_params(&p, 1, view, world, max_rows, hidden, T, hidden, mode, weight, eps, dev_status);
+  if (r != DF_OK) return r;
+  const df::RegionLayout l = df::region_layout(max_rows, hidden);
+  const __nv_bfloat16* mc_partial = reinterpret_cast<const __nv_bfloat16*>(static_cast<uint8_t*>(mc_region) + l.partial_off);
+  __nv_bfloat16* mc_sum = reinterpret_cast<__nv_bfloat16*>(static_cast<uint8_t*>(mc_region) + l.sum_off);
+  size_t smem = (fuse && hidden <= df::kMaxSmemHidden) ? static_cast<size_t>(hidden) * 2 : 0;
+  if (df::g_exclusive_smem > 0) {
+    smem += static_cast<size_t>(df::g_exclusive_smem);
+    const cudaError_t ae =
+        fuse ? cudaFuncSetAttribute(df::allreduce_multicast_kernel<df::EPI_ADD_RMSNORM_SHARDED>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem))
+             : cudaFuncSetAttribute(df::allreduce_multicast_kernel<df::EPI_NONE>,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (ae != cudaSuccess) return df::fail(DF_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(ae));
+  }
+  const int ctas = df::clamp_ctas(n_ctas);
+  if (fuse) {
+    df::allreduce_multicast_kernel<df::EPI_ADD_RMSNORM_SHARDED>
+        <<<ctas, df::kCommThreads, smem, static_cast<cudaStream_t>(stream)>>>(p, mc_partial, mc_sum);
+  } else {
+    df::allreduce_multicast_kernel<df::EPI_NONE>
+        <<<ctas, df::kCommThreads, smem, static_cast<cudaStream_t>(stream)>>>(p, mc_partial, mc_sum);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return df::fail(DF_ECUDA, "multicast all-reduce launch: %s", cudaGetErrorString(e));
+  return DF_OK;
 }
 
 int df_add_rmsnorm_bf16(const void* y, const void* residual_in, void* residual_out, void* out, const void* weight,

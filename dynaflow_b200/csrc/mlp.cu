@@ -516,7 +516,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     // ---------------------------------------------------------- epilogue
     const int q = warp - 4;  // == warp % 4: the TMEM lane quarter this warp may read
     int it = 0;
-    int sk_pending = 0, sk_tile[2] = {0, 0}, sk_n0[2] = {0, 0};  // SKINNY stream-K: tiles this CTA delivered partial sums for
+    int sk_pending = 0, sk_tile[2] = {0, 0}, sk_n0[2] = {0, 0}, sk_mblk[2] = {0, 0};  // stream-K: tiles this CTA delivered partial sums for
     SegmentIter segs(p, rows_tiles_m, rows_num_tiles, unit, num_units, FUSED);
     Segment sg;
     for (; segs.next<ROLE_EPILOGUE>(sg, ring, dl, lane); ++it) {
@@ -600,69 +600,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         continue;
       }
 
-      // ---- stream-K: a segment that does not start at k = 0 only delivers its fp32 partial
-      // sums; the CTA that owns the tile's first k-blocks (it reaches them last) adds the
-      // partials of the later segments, in k order, before its own epilogue.
-      int sk_others = 0;
-      if (CTAS == 1 && p.sk_per > 0) {
-        if (sg.kb0 > 0) {
-          float* mine = p.sk_partials + static_cast<size_t>(unit) * (ACC_COLS * BM);
+      // ---- stream-K: a segment that is not a whole tile only delivers its fp32 partial sums,
+      // [256 accumulator columns][128 rows] per slot (slot 0 for a segment that starts inside a
+      // tile, slot 1 for one that starts a tile); the tile is finished after the segment loop.
+      if (CTAS == 1 && p.sk_per > 0 && !(sg.kb0 == 0 && sg.kb1 == p.num_kb)) {
+        float* mine = p.sk_partials + static_cast<size_t>(2 * unit + (sg.kb0 > 0 ? 0 : 1)) * (ACC_COLS * BM);
 #pragma unroll 1
-          for (int c = 0; c < ACC_COLS / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32(t_acc + c * 32, r);
-            tmem_ld_wait();
-            if (row < rows_m) {
+        for (int c = 0; c < ACC_COLS / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_acc + c * 32, r);
+          tmem_ld_wait();
+          if (row < rows_m) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) mine[(c * 32 + j) * BM + row_in_tile] = __uint_as_float(r[j]);
-            }
-          }
-          tc_fence_before();
-          mbar_arrive(&tempty[acc]);
-          __threadfence();
-          epilogue_bar_sync();
-          if (threadIdx.x == 4 * 32) atomicAdd(p.sk_counters + t, 1u);
-          continue;
-        }
-        if (sg.kb1 < p.num_kb) {
-          // number of later CTAs that hold k-blocks of this tile
-          const long long last_unit = static_cast<long long>(t + 1) * p.num_kb - 1;
-          sk_others = static_cast<int>(last_unit / p.sk_per) - unit;
-          if (threadIdx.x == 4 * 32) {
-            uint32_t spins = 0;
-            while (ld_acquire_gpu(p.sk_counters + t) < static_cast<unsigned>(sk_others)) {
-              if ((++spins & 0xffu) == 0u) {
-                if (*dl.abort) break;
-                if (globaltimer_ns() > dl.t_end) {
-                  *dl.abort = 1u;
-                  report(dl.status, 1u, WHERE_SK_PARTIALS, static_cast<unsigned>(t));
-                  break;
-                }
-              }
-            }
-          }
-          epilogue_bar_sync();
-          if (*dl.abort) break;
-          // fold the partial sums into the accumulator in tensor memory, 32 columns at a time;
-          // the epilogue below then runs unchanged
-#pragma unroll 1
-          for (int c = 0; c < ACC_COLS / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32(t_acc + c * 32, r);
-            tmem_ld_wait();
-            if (row < rows_m) {
-#pragma unroll 1  // (unrolling costs 32 registers, which the co-resident reduction kernel needs)
-              for (int o2 = 1; o2 <= sk_others; ++o2) {
-                const float* part = p.sk_partials + static_cast<size_t>(unit + o2) * (ACC_COLS * BM) + row_in_tile;
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(part + (c * 32 + j) * BM));
-              }
-            }
-            tmem_st_32x32(t_acc + c * 32, r);
-            tmem_st_wait();
+            for (int j = 0; j < 32; ++j) mine[(c * 32 + j) * BM + row_in_tile] = __uint_as_float(r[j]);
           }
         }
+        tc_fence_before();
+        mbar_arrive(&tempty[acc]);
+        __threadfence();
+        epilogue_bar_sync();
+        if (threadIdx.x == 4 * 32) atomicAdd(p.sk_counters + t, 1u);
+        if (sk_pending < 2) {
+          sk_tile[sk_pending] = t;
+          sk_n0[sk_pending] = n0;
+          sk_mblk[sk_pending] = m_blk;
+        }
+        ++sk_pending;
+        continue;
       }
 
       if (tmode == MODE_GATEUP) {
@@ -730,6 +694,105 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[acc]), 0u));
       } else {
         mbar_arrive(&tempty[acc]);
+      }
+    }
+    if (!SKINNY && CTAS == 1 && sk_pending > 0 && !*abort_flag) {
+      // Finish the tiles this CTA holds partial sums of (see the operand-swapped form below for
+      // the protocol). Here a thread owns one row of the tile; the tile's output columns, in
+      // groups of eight, are shared out among the S contributors, and each group is summed over
+      // the S partials in k order, four partials in flight at a time.
+      const int tid = static_cast<int>(threadIdx.x) - 4 * 32;
+      constexpr int GROUPS = (MODE == MODE_GATEUP) ? 16 : 32;  // groups of 8 output columns per tile
+      for (int k = 0; k < (sk_pending < 2 ? sk_pending : 2); ++k) {
+        const int t = sk_tile[k];
+        const int first = static_cast<int>((static_cast<long long>(t) * p.num_kb) / p.sk_per);
+        const int last = static_cast<int>((static_cast<long long>(t + 1) * p.num_kb - 1) / p.sk_per);
+        const int S = last - first + 1;
+        const int s_idx = unit - first;
+        if (tid == 0) {
+          uint32_t spins = 0;
+          while (ld_acquire_gpu(p.sk_counters + t) < static_cast<unsigned>(S)) {
+            if ((++spins & 0xffu) == 0u) {
+              if (*dl.abort) break;
+              if (globaltimer_ns() > dl.t_end) {
+                *dl.abort = 1u;
+                report(dl.status, 1u, WHERE_SK_PARTIALS, static_cast<unsigned>(t));
+                break;
+              }
+            }
+          }
+        }
+        epilogue_bar_sync();
+        if (*dl.abort) break;
+        const int row = sk_mblk[k] * Cfg::kTileM + tid;
+        if (row >= rows_m || (p.debug & 2)) continue;
+        const int g_lo = s_idx * GROUPS / S, g_hi = (s_idx + 1) * GROUPS / S;
+        // partial o of the tile: contributor first + o; o = 0 started the tile (slot 1), the others slot 0
+        const float* base = p.sk_partials + static_cast<size_t>(2 * first) * (ACC_COLS * BM) + tid;
+        __nv_bfloat16* crow = p.C + static_cast<size_t>(row) * p.ldc;
+#pragma unroll 1
+        for (int g = g_lo; g < g_hi; ++g) {
+          const float* src = base + static_cast<size_t>(g * 8) * BM;
+          float a[8], b[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            a[j] = __ldcg(src + ACC_COLS * BM + j * BM);
+            if (MODE == MODE_GATEUP) b[j] = __ldcg(src + ACC_COLS * BM + (128 + j) * BM);
+          }
+          constexpr int AT_ONCE = (MODE == MODE_GATEUP) ? 2 : 4;
+          int o = 1;
+#pragma unroll 1
+          for (; o + AT_ONCE <= S; o += AT_ONCE) {
+            float va[AT_ONCE][8], vb[AT_ONCE][8];
+#pragma unroll
+            for (int w = 0; w < AT_ONCE; ++w) {
+              const float* so = src + static_cast<size_t>(o + w) * (2 * ACC_COLS * BM);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                va[w][j] = __ldcg(so + j * BM);
+                if (MODE == MODE_GATEUP) vb[w][j] = __ldcg(so + (128 + j) * BM);
+              }
+            }
+#pragma unroll
+            for (int w = 0; w < AT_ONCE; ++w) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                a[j] += va[w][j];
+                if (MODE == MODE_GATEUP) b[j] += vb[w][j];
+              }
+            }
+          }
+#pragma unroll 1
+          for (; o < S; ++o) {
+            const float* so = src + static_cast<size_t>(o) * (2 * ACC_COLS * BM);
+            float va[8], vb[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              va[j] = __ldcg(so + j * BM);
+              if (MODE == MODE_GATEUP) vb[j] = __ldcg(so + (128 + j) * BM);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              a[j] += va[j];
+              if (MODE == MODE_GATEUP) b[j] += vb[j];
+            }
+          }
+          const int col = sk_n0[k] + g * 8;
+          if (col < p.N) {
+            uint32_t o4[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (MODE == MODE_GATEUP) {
+                const float g0 = round_bf16(a[2 * j]), g1 = round_bf16(a[2 * j + 1]);
+                const float u0 = round_bf16(b[2 * j]), u1 = round_bf16(b[2 * j + 1]);
+                o4[j] = pack_bf16x2((g0 / (1.0f + expf(-g0))) * u0, (g1 / (1.0f + expf(-g1))) * u1);
+              } else {
+                o4[j] = pack_bf16x2(a[2 * j], a[2 * j + 1]);
+              }
+            }
+            *reinterpret_cast<uint4*>(crow + col) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+          }
+        }
       }
     }
     if (SKINNY && sk_pending > 0 && !*abort_flag) {
@@ -961,7 +1024,7 @@ static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b0, con
     const long long total = static_cast<long long>(p.num_tiles) * p.num_kb;
     // a launch that streams the weights once (few rows) is bound by the bytes in flight: every SM counts
     const double eff_min = 0.01 * tuning_int(skinny ? "DF_GEMM_SK_EFF_SKINNY" : "DF_GEMM_SK_EFF", 60);
-    if (eff < eff_min && p.num_tiles <= units && p.num_kb >= 8 &&
+    if (eff < eff_min && (p.num_tiles <= units || tuning_int("DF_GEMM_SK_WAVES", 0) != 0) && p.num_kb >= 8 &&
         static_cast<size_t>(p.num_tiles) * 4 <= kSkCounterBytes - 64) {
       long long g = units;
       if (g > total / 4) g = total / 4;  // at least four k-blocks per CTA

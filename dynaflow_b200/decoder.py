@@ -25,7 +25,7 @@ import torch
 import torch.nn.functional as F
 
 from . import _native, ops
-from .comm import PeerComm, add_rmsnorm
+from .comm import MulticastComm, PeerComm, add_rmsnorm
 
 
 @dataclasses.dataclass
@@ -43,7 +43,8 @@ class DecoderShape:
 
 class TensorParallelDecoder:
     def __init__(self, shape: DecoderShape, *, rank: int = 0, world: int = 1, max_rows: int, micro_batches: int = 2,
-                 seed: int = 0, device: torch.device | None = None, weights: dict | None = None, n_ctas: int = 32) -> None:
+                 seed: int = 0, device: torch.device | None = None, weights: dict | None = None, n_ctas: int = 32,
+                 multicast: bool = False, gemm_max_ctas: int = 0) -> None:
         s = shape
         if s.heads % world or s.kv_heads % world or s.intermediate % world:
             raise ValueError("heads, kv heads and the intermediate size must divide evenly across ranks")
@@ -95,7 +96,9 @@ class TensorParallelDecoder:
         self.x = [torch.empty(max_rows, s.hidden, dtype=torch.bfloat16, device=dev) for _ in range(n)]
         self.residual = [torch.empty(max_rows, s.hidden, dtype=torch.bfloat16, device=dev) for _ in range(n)]
         self.partial_local = [torch.empty(max_rows, s.hidden, dtype=torch.bfloat16, device=dev) for _ in range(n)]
-        self.comm = PeerComm(rank, world, max_rows, s.hidden, slots=n, n_ctas=n_ctas, device=dev) if world > 1 else None
+        comm_cls = MulticastComm if multicast else PeerComm   # in-switch or peer-memory reduction
+        self.comm = comm_cls(rank, world, max_rows, s.hidden, slots=n, n_ctas=n_ctas, device=dev) if world > 1 else None
+        self.gemm_max_ctas = gemm_max_ctas                    # CTAs the GEMMs may use (0 = one per SM)
         self.launch_count = 0
 
     # ------------------------------------------------------------------ pieces
@@ -106,7 +109,7 @@ class TensorParallelDecoder:
         s = self.s
         rows = batch * seq
         qkv = self.qkv[mb][:rows]
-        ops.gemm_bf16(x, layer["wqkv"], out=qkv)
+        ops.gemm_bf16(x, layer["wqkv"], out=qkv, max_ctas=self.gemm_max_ctas)
         rc = self.lib.df_rope_bf16(qkv.data_ptr(), pos.data_ptr(), rows, self.qh + self.kvh, s.head_dim, qkv.stride(0),
                                    s.rope_theta, torch.cuda.current_stream(self.device).cuda_stream)
         if rc != 0:
@@ -117,11 +120,12 @@ class TensorParallelDecoder:
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.qh != self.kvh)
         attn = self.attn_out[mb][:rows]
         attn.view(batch, seq, self.qh, s.head_dim).copy_(o.transpose(1, 2))
-        ops.gemm_bf16(attn, layer["wo"], out=self._partial(mb, rows))
+        ops.gemm_bf16(attn, layer["wo"], out=self._partial(mb, rows), max_ctas=self.gemm_max_ctas)
         self.launch_count += 3
 
     def _mlp_half(self, layer: dict, x: torch.Tensor, mb: int, rows: int) -> None:
-        ops.gated_mlp(x, layer["wg"], layer["wu"], layer["wd"], out=self._partial(mb, rows), workspace=self.workspace[mb])
+        ops.gated_mlp(x, layer["wg"], layer["wu"], layer["wd"], out=self._partial(mb, rows), workspace=self.workspace[mb],
+                      max_ctas=self.gemm_max_ctas)
         self.launch_count += 2
 
     def _reduce_norm(self, mb: int, rows: int, weight: torch.Tensor, first: bool = False) -> torch.Tensor:

@@ -62,6 +62,11 @@ class TensorParallelGatedMLP:
         if world > 1 and comm is None:
             raise ValueError("world > 1 needs a communicator (dynaflow_b200.comm.PeerComm)")
         self.launches_per_step = 2 * micro_batches + (micro_batches if world > 1 else 0)
+        # CTAs the GEMMs may use (0 = one per SM). Fewer leaves whole SMs to the reduction that
+        # runs beside the next micro-batch's GEMMs.
+        self.gemm_max_ctas = 0
+        # per slot: the event after which the slot's partial-output buffer may be overwritten
+        self._slot_free: list[torch.cuda.Event | None] = [None] * micro_batches
 
     # ------------------------------------------------------------------
     def _mlp(self, x: torch.Tensor, out: torch.Tensor, mb: int, record: bool):
@@ -71,24 +76,30 @@ class TensorParallelGatedMLP:
         if record:
             m0, m1, m2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
             m0.record()
-            ops.gateup_silu(x, self.w_gate, self.w_up, out=h)
+            ops.gateup_silu(x, self.w_gate, self.w_up, out=h, max_ctas=self.gemm_max_ctas)
             m1.record()
-            ops.gemm_bf16(h, self.w_down, out=out)
+            ops.gemm_bf16(h, self.w_down, out=out, max_ctas=self.gemm_max_ctas)
             m2.record()
             marks = (m0, m1, m2)
         else:
-            ops.gated_mlp(x, self.w_gate, self.w_up, self.w_down, out=out, workspace=self.workspaces[mb])
+            ops.gated_mlp(x, self.w_gate, self.w_up, self.w_down, out=out, workspace=self.workspaces[mb],
+                          max_ctas=self.gemm_max_ctas)
         return marks
 
     def forward_device(self, x: torch.Tensor, out: torch.Tensor, cuts: list[int], record_kernel_events: bool = False,
-                       results: list | None = None, skip_comm: bool = False, skip_compute: bool = False):
+                       results: list | None = None, skip_comm: bool = False, skip_compute: bool = False,
+                       join: bool = True):
         """Runs ``mlp(x[cuts[i]:cuts[i+1]])`` for every micro-batch ``i`` on the current stream.
 
         Single rank: the rows land in ``out``. Tensor parallel: each micro-batch's partial
         output is written straight into the communicator's region and reduced on the
         communication stream while the next micro-batch's GEMMs run; the reduced rows
         are then ``comm.result(slot, rows)`` (appended to ``results`` if given), and the
-        current stream waits for the last reduction before the call returns.
+        current stream waits for the last reduction before the call returns -- unless
+        ``join=False``: then consecutive calls pipeline the way consecutive layers do, the last
+        micro-batch's reduction running under the next call's first GEMMs (each GEMM waits only
+        for the previous reduction out of its own slot, whose buffer it overwrites), and the
+        caller joins with ``wait_reductions()`` before reading a result.
         ``skip_comm`` / ``skip_compute`` run the same schedule with the reductions, resp. the
         GEMMs, left out (measurement of how much communication the overlap hides)."""
         marks = []
@@ -99,6 +110,9 @@ class TensorParallelGatedMLP:
                 continue
             slot = mb % self.micro_batches
             target = out[lo:hi] if self.world == 1 else self.comm.partial(slot, hi - lo)
+            if self.world > 1 and self._slot_free[slot] is not None:
+                main.wait_event(self._slot_free[slot])
+                self._slot_free[slot] = None
             if not skip_compute:
                 m = self._mlp(x[lo:hi], target, slot, record_kernel_events)
                 if m is not None:
@@ -109,17 +123,27 @@ class TensorParallelGatedMLP:
                 self.comm.stream.wait_event(ready)
                 with torch.cuda.stream(self.comm.stream):
                     reduced = self.comm.all_reduce(slot, hi - lo)
+                    freed = torch.cuda.Event()
+                    freed.record(self.comm.stream)
+                self._slot_free[slot] = freed
                 if results is not None:
                     results.append(reduced)
             elif results is not None:
                 results.append(target)
-        if self.world > 1:
-            main.wait_stream(self.comm.stream)
+        if self.world > 1 and join:
+            self.wait_reductions()
         return marks
+
+    def wait_reductions(self) -> None:
+        """Makes the current stream wait for every reduction issued so far."""
+        if self.world > 1:
+            torch.cuda.current_stream(self.device).wait_stream(self.comm.stream)
+            self._slot_free = [None] * self.micro_batches
 
     def forward_chain(self, x: torch.Tensor, cuts: list[int], layers: int, norm_weight: torch.Tensor,
                       residual: torch.Tensor, skip_comm: bool = False, skip_compute: bool = False,
-                      fused_norm: bool = True, sharded_residual: bool = False) -> list[torch.Tensor]:
+                      fused_norm: bool = True, sharded_residual: bool = False,
+                      timings: list | None = None) -> list[torch.Tensor]:
         """``layers`` tensor-parallel MLP blocks back to back, the way a decoder runs them: for
         every micro-batch ``x <- rmsnorm(allreduce(mlp(x)) + residual) * w`` with the fused
         reduction kernel on the communication stream, so that the reduction of micro-batch
@@ -129,7 +153,8 @@ class TensorParallelGatedMLP:
         sharded by rows and the add + RMSNorm happen inside the reduction, between its two
         shots; the block's output is then the communicator's result buffer, which the next
         block's reduction of the same micro-batch overwrites -- after that block's GEMMs have
-        consumed it. Returns the per-micro-batch outputs."""
+        consumed it. Returns the per-micro-batch outputs. ``timings``, if given, receives one
+        ``(kind, start_event, end_event)`` per GEMM pair ("mlp") and per reduction ("reduce")."""
         assert self.world > 1 and self.comm is not None
         main = torch.cuda.current_stream(self.device)
         comm_stream = self.comm.stream
@@ -148,20 +173,32 @@ class TensorParallelGatedMLP:
                 if reduced[mb] is not None:
                     main.wait_event(reduced[mb])          # this micro-batch's input is the previous block's output
                 if not skip_compute:
+                    if timings is not None:
+                        t0 = torch.cuda.Event(enable_timing=True)
+                        t0.record(main)
                     self._mlp(xs[mb], self.comm.partial(slot, rows), slot, False)
+                    if timings is not None:
+                        t1 = torch.cuda.Event(enable_timing=True)
+                        t1.record(main)
+                        timings.append(("mlp", t0, t1))
                 ready = torch.cuda.Event()
                 ready.record(main)
                 if not skip_comm:
                     comm_stream.wait_event(ready)
                     with torch.cuda.stream(comm_stream):
+                        if timings is not None:
+                            c0 = torch.cuda.Event(enable_timing=True)
+                            c0.record(comm_stream)
                         if sharded_residual:
                             nxt = self.comm.all_reduce_add_rmsnorm_sharded(slot, rows, res[mb], norm_weight)
                         else:
                             self.comm.all_reduce_add_rmsnorm(slot, rows, res[mb], norm_weight, outs[mb], res[mb],
                                                              fused=fused_norm)
                             nxt = outs[mb]
-                        done = torch.cuda.Event()
+                        done = torch.cuda.Event(enable_timing=timings is not None)
                         done.record(comm_stream)
+                        if timings is not None:
+                            timings.append(("reduce", c0, done))
                     reduced[mb] = done
                     xs[mb] = nxt
                     if sharded_residual:

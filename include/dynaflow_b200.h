@@ -209,6 +209,30 @@ int df_allreduce_add_rmsnorm_sharded_bf16(const df_comm_rank_t* view, int world,
                                           const void* weight, float eps, int n_ctas, df_status_t* dev_status,
                                           void* stream);
 
+/* Process-wide: shared memory every reduction CTA of the calls above and below claims beyond what
+ * it uses (0, the default, = none). With 40960 a reduction CTA cannot share an SM with a CTA of
+ * the GEMM kernels (which hold 197 KB of the SM's 227 KB), nor the other way round: if the GEMMs
+ * are launched with max_ctas = SMs - k, the reduction runs on the k SMs they leave free (two of
+ * its CTAs per SM) instead of sharing SMs, and their memory traffic, with the GEMM CTAs. If no
+ * SM is free the reduction simply starts when GEMM CTAs retire. No counterpart in the reference,
+ * whose all-reduce runs on whatever SMs NCCL's kernel is given. */
+int df_comm_set_exclusive_smem(int bytes);
+
+/* The all-reduce (fuse = 0) and the sharded-residual fused form (fuse = 1) with the reduction
+ * done inside the NVLink switch: `mc_region` is the multicast address of the SAME region that
+ * view->regions[r] are the per-rank addresses of (an NVLink multicast object bound to every
+ * rank's region, e.g. torch.distributed._symmetric_memory's multicast_ptr; region size and
+ * layout as for the calls above). The owner of a row slice reads it with multimem.ld_reduce
+ * (summed over all ranks by the switch, fp32 accumulation, rounded to bf16 once) and delivers
+ * the result to every rank with multimem.st; the flag barriers still go through the per-rank
+ * addresses. The order of the switch's summation is not the rank order of df_allreduce_bf16, so
+ * results can differ from it in the last bf16 bit; they are identical on every rank.
+ * (tokenweave.cu:38-113, the reference's fused all-reduce + RMSNorm, is built on the same
+ * instructions.) weight / eps are unused when fuse = 0. */
+int df_allreduce_multicast_bf16(const df_comm_rank_t* view, void* mc_region, int world, int max_rows, int hidden, int T,
+                                int fuse, const void* weight, float eps, int n_ctas, df_status_t* dev_status,
+                                void* stream);
+
 /* The second half of the fused call as its own launch over all SMs:
  * r' = y + residual_in (NULL = zeros); out = bf16(r' * rsqrt(mean(r'^2) + eps)) * weight;
  * residual_out = r' (may equal residual_in). The RMSNorm(+residual) module a host model

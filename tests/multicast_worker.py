@@ -1,0 +1,91 @@
+"""Worker of tests/test_gpu_multi.py::test_multicast_allreduce: launched by torch.distributed.run, one rank
+per GPU. Every rank reaches the final barrier and closes its communicator whether its checks passed or not
+(a rank that leaves early while its memory is bound to the multicast object can fault the others' GPUs)."""
+import os
+import sys
+import traceback
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+
+def checks(comm, rank: int, world: int, dev: torch.device) -> None:
+    from dynaflow_b200 import ops
+    from oracle import ops_oracle
+
+    T, H = 1000, 1024
+    parts = [torch.randn(T, H, generator=torch.Generator().manual_seed(100 + r)).bfloat16() for r in range(world)]
+    acc = torch.zeros(T, H)
+    for p in parts:
+        acc += p.float()
+    want = acc.bfloat16()
+    # ---- all-reduce inside the switch: within one bf16 rounding of the fp32 sum, identical on every rank
+    for call in range(3):
+        comm.partial(0, T).copy_(parts[rank])
+        got = comm.all_reduce(0, T)
+        torch.cuda.synchronize()
+        ops.check_status()
+        rel = ((got.cpu().float() - want.float()).abs().max() / want.float().abs().max()).item()
+        assert rel <= 2e-2, f"rank {rank} call {call}: multicast all-reduce rel err {rel}"
+        exact = (got.cpu() == want).float().mean().item()
+        assert exact >= 0.9, f"rank {rank} call {call}: only {exact:.3f} of the elements equal the fp32 sum"
+        digest = got.view(torch.int16).to(torch.int64).sum().reshape(1)
+        all_digests = [torch.zeros_like(digest) for _ in range(world)]
+        dist.all_gather(all_digests, digest)
+        assert all(int(d.item()) == int(digest.item()) for d in all_digests), "ranks hold different results"
+    # ---- sharded-residual fused form (reduce-scatter in the switch, add + RMSNorm on the owned rows, broadcast)
+    g = torch.Generator().manual_seed(5)
+    residual = torch.randn(T, H, generator=g).bfloat16()
+    weight = (1 + 0.1 * torch.randn(H, generator=g)).bfloat16()
+    want_out, want_res = ops_oracle.allreduce_add_rmsnorm(parts, residual, weight)
+    comm.partial(1, T).copy_(parts[rank])
+    res_dev = residual.to(dev)
+    out = comm.all_reduce_add_rmsnorm_sharded(1, T, res_dev, weight.to(dev))
+    torch.cuda.synchronize()
+    ops.check_status()
+    rel = ((out.float().cpu() - want_out.float()).abs().max() / want_out.float().abs().max()).item()
+    assert rel <= 2e-2, f"rank {rank}: fused RMSNorm rel err {rel}"
+    lo, hi = comm.slice_bounds(T)
+    rel = ((res_dev[lo:hi].cpu().float() - want_res[lo:hi].float()).abs().max() / want_res.float().abs().max()).item()
+    assert rel <= 2e-2, f"rank {rank}: residual slice rel err {rel}"
+    # an empty slice on some ranks (fewer rows than ranks) and a second slot in flight right after
+    comm.partial(0, 3).copy_(parts[rank][:3])
+    got = comm.all_reduce(0, 3)
+    torch.cuda.synchronize()
+    ops.check_status()
+    rel = ((got.cpu().float() - want[:3].float()).abs().max() / want[:3].float().abs().max()).item()
+    assert rel <= 2e-2, f"rank {rank}: 3-row multicast all-reduce rel err {rel}"
+
+
+def main() -> None:
+    from dynaflow_b200.comm import MulticastComm
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    comm = MulticastComm(rank, world, max_rows=1024, hidden=1024, slots=2, n_ctas=16, device=dev)
+    failed = torch.zeros(1, device=dev)
+    try:
+        checks(comm, rank, world, dev)
+    except Exception:  # noqa: BLE001 -- reported below, after every rank has left together
+        traceback.print_exc()
+        failed += 1
+    dist.all_reduce(failed)
+    torch.cuda.synchronize()
+    dist.barrier()
+    comm.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    if rank == 0 and failed.item() == 0:
+        print("MULTICAST_OK")
+    sys.exit(0 if failed.item() == 0 else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -28,3 +28,17 @@ def test_peer_allreduce_and_tp_layer(world):
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert proc.returncode == 0, (proc.stdout[-3000:], proc.stderr[-3000:])
     assert "MULTI_GPU_OK" in proc.stdout
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_multicast_allreduce(world):
+    """The in-switch form of the reduction (multimem.ld_reduce / multimem.st over an NVLink
+    multicast mapping) against the fp32 sum and the oracle's fused residual + RMSNorm."""
+    if _gpus() < world:
+        pytest.skip(f"needs {world} GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29520 + world),
+           os.path.join(ROOT, "tests", "multicast_worker.py")]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, (proc.stdout[-3000:], proc.stderr[-3000:])
+    assert "MULTICAST_OK" in proc.stdout
