@@ -33,7 +33,9 @@ if ROOT not in sys.path:
 H, I = 4096, 14336
 ROWS = 16384
 MICRO_BATCHES = 2
-GATEUP_DRAM_BYTES_PER_LAUNCH = 788_613_632
+# dram__bytes_read.sum + dram__bytes_write.sum of one MLP launch (8192 rows, one GPU) from the 1-pass ncu capture
+# summarised under profiles/; None until such a capture of the single-launch kernel exists
+MLP_DRAM_BYTES_PER_LAUNCH = None
 METRIC = "prefill tokens/sec through the fused gated-MLP layer (2 micro-batches)"
 
 
@@ -261,8 +263,13 @@ def run_ours(args) -> None:
     barrier()
     t_wall1 = time.time()
     ms_step = max_over_ranks(start.elapsed_time(end) / args.steps)
-    gateup_ms = statistics.mean(m0.elapsed_time(m1) for step in marks for (m0, m1, _m2) in step)
-    down_ms = statistics.mean(m1.elapsed_time(m2) for step in marks for (_m0, m1, m2) in step)
+    mlp_ms = statistics.mean(m0.elapsed_time(m1) for step in marks for (m0, m1) in step)
+    ops.check_status()
+    # the same MLP as two launches, a few steps outside the timed region: how the time splits between the GEMMs
+    split = [layer.forward_device(x_dev, out_dev, cuts, record_kernel_events="split") for _ in range(max(3, args.steps // 10))]
+    barrier()
+    gateup_ms = statistics.mean(m0.elapsed_time(m1) for step in split for (m0, m1, _m2) in step)
+    down_ms = statistics.mean(m1.elapsed_time(m2) for step in split for (_m0, m1, m2) in step)
     ops.check_status()
 
     # ---- N > 1: how much of the reduction hides under the other micro-batch's GEMMs
@@ -335,13 +342,13 @@ def run_ours(args) -> None:
 
     peaks, peak_kind = measured_peaks()
     rows_mb = ROWS // MICRO_BATCHES
-    gateup_flops = 4.0 * rows_mb * H * (I // world)
-    achieved = gateup_flops / (gateup_ms * 1e-3) / 1e12
-    peak = float(peaks["bf16_tflops"])
+    mlp_flops = 6.0 * rows_mb * H * (I // world)          # one launch: gate/up 4 M H I + down 2 M H I
+    achieved = mlp_flops / (mlp_ms * 1e-3) / 1e12
+    # the kernel is timed inside the long step, under the power cap: the sustained cuBLAS figure is its denominator
+    burst = float(peaks["bf16_tflops"])
+    peak = float(peaks.get("bf16_tflops_sustained", burst))
     step_flops = 6.0 * ROWS * H * (I // world)
-    # dram__bytes_read.sum + dram__bytes_write.sum of one gate/up launch at 8192 rows, from the 1-pass ncu
-    # capture summarised in profiles/gated_mlp_launch_list_rows16384.md; it only describes that shape
-    traffic = GATEUP_DRAM_BYTES_PER_LAUNCH if (ROWS == 16384 and world == 1) else None
+    traffic = MLP_DRAM_BYTES_PER_LAUNCH if (ROWS == 16384 and world == 1) else None
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
@@ -365,14 +372,17 @@ def run_ours(args) -> None:
         "e2e": {"value": ROWS / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": ROWS * H * 2, "d2h_bytes_per_step": ROWS * H * 2},
         "gpu_launches": layer.launches_per_step * args.steps,
-        "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel<GATEUP> (gate/up GEMM + SiLU*mul epilogue)",
+        "roofline": {"bound": "tensor",
+                     "kernel": "gemm_tc_kernel<FUSED> (gate/up GEMM + SiLU*mul epilogue + down GEMM, one persistent launch)",
                      "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                     "peak_source": f"{peak_kind} cuBLAS bf16 burst", "frac_of_sustained":
-                         achieved / float(peaks.get("bf16_tflops_sustained", peak)),
+                     "peak_source": f"{peak_kind} cuBLAS bf16, sustained loop (kernel timed inside the long step)",
+                     "frac_of_burst": achieved / burst, "burst_peak": burst,
                      "frac_of_nominal_2250": achieved / 2250.0, "traffic": traffic,
-                     "flops_per_launch": gateup_flops, "ms_per_launch": gateup_ms,
-                     "down_gemm_tflops": 2.0 * rows_mb * H * (I // world) / (down_ms * 1e-3) / 1e12},
-        "mlp_pct_tensor_peak": 100.0 * step_flops / (ms_step * 1e-3) / 1e12 / peak,
+                     "flops_per_launch": mlp_flops, "ms_per_launch": mlp_ms,
+                     "as_two_launches": {"gateup_ms": gateup_ms, "down_ms": down_ms,
+                                         "gateup_tflops": 4.0 * rows_mb * H * (I // world) / (gateup_ms * 1e-3) / 1e12,
+                                         "down_tflops": 2.0 * rows_mb * H * (I // world) / (down_ms * 1e-3) / 1e12}},
+        "mlp_pct_tensor_peak": 100.0 * step_flops / (ms_step * 1e-3) / 1e12 / burst,
         "clocks": sampler.summary(t_wall0, t_wall1) if sampler is not None else None,
         "cpu_baseline": cpu,
         "sweep": sweep,

@@ -61,7 +61,9 @@ class TensorParallelGatedMLP:
         self.comm = comm
         if world > 1 and comm is None:
             raise ValueError("world > 1 needs a communicator (dynaflow_b200.comm.PeerComm)")
-        self.launches_per_step = 2 * micro_batches + (micro_batches if world > 1 else 0)
+        # kernels of this library per step at the benchmark's shapes: one persistent MLP launch per
+        # micro-batch (two below a wave of tiles) plus one reduction per micro-batch
+        self.launches_per_step = micro_batches + (micro_batches if world > 1 else 0)
         # CTAs the GEMMs may use (0 = one per SM). Fewer leaves whole SMs to the reduction that
         # runs beside the next micro-batch's GEMMs.
         self.gemm_max_ctas = 0
@@ -73,7 +75,8 @@ class TensorParallelGatedMLP:
         rows = x.shape[0]
         h = self.h_views[mb][:rows]
         marks = None
-        if record:
+        if record == "split":
+            # the two GEMMs as separate launches, an event between them (measurement of the split only)
             m0, m1, m2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
             m0.record()
             ops.gateup_silu(x, self.w_gate, self.w_up, out=h, max_ctas=self.gemm_max_ctas)
@@ -81,16 +84,25 @@ class TensorParallelGatedMLP:
             ops.gemm_bf16(h, self.w_down, out=out, max_ctas=self.gemm_max_ctas)
             m2.record()
             marks = (m0, m1, m2)
+        elif record:
+            m0, m1 = (torch.cuda.Event(enable_timing=True) for _ in range(2))
+            m0.record()
+            ops.gated_mlp(x, self.w_gate, self.w_up, self.w_down, out=out, workspace=self.workspaces[mb],
+                          max_ctas=self.gemm_max_ctas)
+            m1.record()
+            marks = (m0, m1)
         else:
             ops.gated_mlp(x, self.w_gate, self.w_up, self.w_down, out=out, workspace=self.workspaces[mb],
                           max_ctas=self.gemm_max_ctas)
         return marks
 
-    def forward_device(self, x: torch.Tensor, out: torch.Tensor, cuts: list[int], record_kernel_events: bool = False,
+    def forward_device(self, x: torch.Tensor, out: torch.Tensor, cuts: list[int], record_kernel_events: bool | str = False,
                        results: list | None = None, skip_comm: bool = False, skip_compute: bool = False,
                        join: bool = True):
         """Runs ``mlp(x[cuts[i]:cuts[i+1]])`` for every micro-batch ``i`` on the current stream.
 
+        ``record_kernel_events``: ``True`` returns a (start, end) event pair around every micro-batch's
+        MLP launch, ``"split"`` runs gate/up and down as two launches with an event between them.
         Single rank: the rows land in ``out``. Tensor parallel: each micro-batch's partial
         output is written straight into the communicator's region and reduced on the
         communication stream while the next micro-batch's GEMMs run; the reduced rows

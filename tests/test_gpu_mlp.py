@@ -219,3 +219,38 @@ def test_one_launch_mlp_equals_two_launches(ops, M, H, I):
     small = ops.gated_mlp(x, wg, wu, wd, max_ctas=5)     # few CTAs: long waits on the panel counters
     ops.check_status()
     assert torch.equal(small, two)
+
+
+@pytest.mark.parametrize("M", [1, 7, 16, 17, 48, 64, 65, 100, 127, 128])
+@pytest.mark.parametrize("H,I", [(4096, 14336), (1024, 2816)])
+def test_decode_rows_operand_swapped_form(ops, M, H, I):
+    """Launches of at most 128 rows take the operand-swapped form of the GEMM kernel (weight rows on
+    the accumulator lanes, token rows on its columns, stream-K partial sums finished cooperatively).
+    Against the oracle, against the regular form, bit-reproducible, and nothing written past row M."""
+    import os
+
+    from oracle import ops_oracle
+
+    x = _rand((M, H), 1.0, 21)
+    wg, wu, wd = _rand((I, H), 0.02, 22), _rand((I, H), 0.02, 23), _rand((H, I), 0.02, 24)
+    dev = [t.cuda() for t in (x, wg, wu, wd)]
+    canvas = torch.full((M + 2, H), 7.0, dtype=torch.bfloat16, device="cuda")   # guard rows after the output
+    out = canvas[:M]
+    ops.gated_mlp(*dev, out=out)
+    first = out.clone()
+    ops.gated_mlp(*dev, out=out)
+    ops.check_status()
+    assert torch.equal(out, first)
+    assert torch.all(canvas[M:] == 7.0)
+    assert rel_err(out, ops_oracle.gated_mlp(x, wg, wu, wd)) <= TOL
+    h = ops.gateup_silu(dev[0], dev[1], dev[2])          # the entry point without a workspace: whole tiles
+    g = torch.nn.functional.linear(x, wg)
+    u = torch.nn.functional.linear(x, wu)
+    assert rel_err(h, ops_oracle.silu_mul(g, u)) <= TOL
+    os.environ["DF_GEMM_SKINNY"] = "0"
+    try:
+        regular = ops.gated_mlp(*dev)
+    finally:
+        os.environ["DF_GEMM_SKINNY"] = "1"
+    ops.check_status()
+    assert rel_err(out, regular) <= 1e-2
