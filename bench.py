@@ -266,10 +266,12 @@ def run_ours(args) -> None:
     mlp_ms = statistics.mean(m0.elapsed_time(m1) for step in marks for (m0, m1) in step)
     ops.check_status()
     # the same MLP as two launches, a few steps outside the timed region: how the time splits between the GEMMs
+    for _ in range(2):
+        layer.forward_device(x_dev, out_dev, cuts, record_kernel_events="split")
     split = [layer.forward_device(x_dev, out_dev, cuts, record_kernel_events="split") for _ in range(max(3, args.steps // 10))]
     barrier()
-    gateup_ms = statistics.mean(m0.elapsed_time(m1) for step in split for (m0, m1, _m2) in step)
-    down_ms = statistics.mean(m1.elapsed_time(m2) for step in split for (_m0, m1, m2) in step)
+    gateup_ms = statistics.median(m0.elapsed_time(m1) for step in split for (m0, m1, _m2) in step)
+    down_ms = statistics.median(m1.elapsed_time(m2) for step in split for (_m0, m1, m2) in step)
     ops.check_status()
 
     # ---- N > 1: how much of the reduction hides under the other micro-batch's GEMMs

@@ -100,7 +100,9 @@ struct GemmParams {
   // tile, are cut into equal ranges of sk_per units, one range per CTA, so that every SM
   // streams its share of the weights even when there are fewer tiles than SMs.
   int sk_per;
-  float* sk_partials;        // [grid][256 columns][128 rows] fp32, column-major per CTA
+  // Two slots of 256 x 128 fp32 per CTA (slot 0: a segment that starts inside a tile, slot 1: one
+  // that starts a tile). Regular form: [accumulator column][row]; operand-swapped form: [row of A][256].
+  float* sk_partials;
   unsigned int* sk_counters;  // [num_tiles] partial segments delivered, zero at launch
   // Dynamic tile order (1-CTA whole-tile launches with a workspace): the first tile of a CTA is
   // its block index, the next ones come from this counter (zero at launch), so a CTA that

@@ -102,10 +102,13 @@ int df_gateup_silu_bf16(const void* x, const void* w_gate, const void* w_up, voi
 
 /* Small-M forms of the two GEMMs. With fewer output tiles than SMs (decode-sized
  * nano-batches) the launch is bound by streaming the weights from HBM, so the
- * k-blocks of all tiles are divided evenly over the SMs ("stream-K"): CTAs that
- * only hold a tile's later k-blocks leave fp32 partial sums in `splitk_ws`, the
- * CTA holding its first k-blocks adds them in k order (deterministic) and runs
- * the epilogue. `splitk_ws` is caller-owned device scratch of at least
+ * k-blocks of all tiles are divided evenly over the SMs ("stream-K"): every CTA
+ * that holds only part of a tile's k-blocks leaves fp32 partial sums in
+ * `splitk_ws`; once all contributors of a tile have delivered, each of them adds
+ * the partial sums of its share of the tile's outputs in k order (deterministic)
+ * and runs the epilogue on them. Launches of at most 128 rows use an
+ * operand-swapped form of the same kernel (weight rows on the accumulator lanes)
+ * with a deeper copy pipeline. `splitk_ws` is caller-owned device scratch of at least
  * df_gemm_splitk_workspace_bytes() bytes, 256-byte aligned, contents arbitrary;
  * launches that can overlap on the GPU need separate workspaces. With
  * splitk_ws == NULL, or when whole tiles already fill the SMs, these behave
