@@ -33,9 +33,9 @@ if ROOT not in sys.path:
 H, I = 4096, 14336
 ROWS = 16384
 MICRO_BATCHES = 2
-# dram__bytes_read.sum + dram__bytes_write.sum of one MLP launch (8192 rows, one GPU) from the 1-pass ncu capture
-# summarised under profiles/; None until such a capture of the single-launch kernel exists
-MLP_DRAM_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one single-launch MLP (8192 rows, one GPU) from the 1-pass ncu
+# capture summarised in profiles/gated_mlp_launch_list_rows16384.md; it only describes that shape
+MLP_DRAM_BYTES_PER_LAUNCH = 1_633_166_336 + 296_816_640
 METRIC = "prefill tokens/sec through the fused gated-MLP layer (2 micro-batches)"
 
 
@@ -536,6 +536,80 @@ def run_decoder(args) -> None:
         dist.destroy_process_group()
 
 
+def run_moe(args) -> None:
+    """Third workload (not the default line): Mixtral-shaped top-2 MoE stack, 16384 tokens per step, 8 experts of
+    intermediate 14336, expert parallel over the launched ranks (one rank: all experts local).
+    value = tokens/s through `--moe-layers` layers (dispatch / expert / combine each)."""
+    import torch
+    import torch.distributed as dist
+
+    from dynaflow_b200 import ops
+    from dynaflow_b200.moe import ExpertParallelMoE
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    experts, tokens, layers = 8, ROWS, args.moe_layers
+    per_rank = tokens // world
+    gen = torch.Generator(device=dev).manual_seed(7)      # same weights on every rank; each keeps its experts
+
+    def weight(*shape):
+        return (torch.randn(*shape, device=dev, generator=gen) * 0.02).bfloat16()
+
+    stack = []
+    for _ in range(layers):
+        w = (weight(experts, I, H), weight(experts, I, H), weight(experts, H, I))
+        stack.append(ExpertParallelMoE(H, I, experts, per_rank, rank=rank, world=world, weights=w, slots=1,
+                                       n_ctas=args.comm_ctas or 32, device=dev))
+        del w
+    x = torch.randn(per_rank, H, device=dev, generator=gen).bfloat16()
+    logits = [torch.randn(per_rank, experts, device=dev, generator=gen).bfloat16() for _ in range(layers)]
+
+    def step():
+        for layer, lg in zip(stack, logits):      # every layer routes the same rows with its own router logits
+            layer.forward(x, lg)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = max(3, args.steps // 10)
+    a.record()
+    for _ in range(reps):
+        step()
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / reps
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ops.check_status()
+    peaks, kind = measured_peaks()
+    flops = 2.0 * tokens * 6.0 * H * I * layers               # two experts per token
+    line = {"workload": f"Mixtral-shaped top-2 MoE, {layers} layers, {experts} experts x {I}, {tokens} tokens per step, ep{world}",
+            "metric": "tokens/sec", "unit": "tokens/s", "n_gpus": world, "ms_per_step": ms, "value": tokens / (ms * 1e-3),
+            "flops_per_step": flops, "tflops_per_gpu": flops / world / (ms * 1e-3) / 1e12,
+            "frac_of_tensor_peak": flops / world / (ms * 1e-3) / 1e12 / float(peaks["bf16_tflops"]),
+            "peak_source": f"{kind} cuBLAS bf16 burst", "steps": reps, "data": "synthetic"}
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
+    for layer in stack:
+        layer.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main() -> None:
     global ROWS
     ap = argparse.ArgumentParser()
@@ -556,7 +630,8 @@ def main() -> None:
                     "of running on SMs of their own")
     ap.add_argument("--replicated-residual", action="store_true",
                     help="N > 1 chain: keep the residual stream replicated on every rank instead of sharded by rows")
-    ap.add_argument("--workload", choices=["mlp", "decoder"], default="mlp",
+    ap.add_argument("--moe-layers", type=int, default=4, help="moe workload: number of layers")
+    ap.add_argument("--workload", choices=["mlp", "decoder", "moe"], default="mlp",
                     help="mlp: the fused gated-MLP layer step (the benchmark line); decoder: a Llama-3-8B-shaped "
                          "decoder prefill on the same kernels (reported separately)")
     ap.add_argument("--layers", type=int, default=32, help="decoder workload: number of layers")
@@ -573,6 +648,8 @@ def main() -> None:
         run_reference_arm(args)
     elif args.workload == "decoder":
         run_decoder(args)
+    elif args.workload == "moe":
+        run_moe(args)
     else:
         run_ours(args)
 
