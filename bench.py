@@ -98,25 +98,27 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------ CPU arm
-def cpu_port_rate(rows: int, repeats: int = 1) -> tuple[float, float]:
-    """Times the oracle's gated MLP (the reference's operator chain restated on
-    PyTorch CPU ops, bf16, all host threads) on ``rows`` rows. Returns (tokens/s, seconds)."""
+def cpu_port_sample(target_seconds: float = 12.0, rows: int = 2048) -> tuple[float, float, int]:
+    """Times the oracle's gated MLP (the reference's operator chain restated on PyTorch CPU ops,
+    bf16, all host threads): passes over the same ``rows`` rows of the workload, after one untimed
+    pass, until ``target_seconds`` of CPU work are done. Returns (tokens/s, seconds, passes)."""
     import torch
 
     from oracle import ops_oracle
 
-    g = torch.Generator().manual_seed(0)
-    x = torch.randn(rows, H, generator=g).bfloat16()
-    wg = (torch.randn(I, H, generator=g) * 0.02).bfloat16()
-    wu = (torch.randn(I, H, generator=g) * 0.02).bfloat16()
-    wd = (torch.randn(H, I, generator=g) * 0.02).bfloat16()
-    best = float("inf")
+    wg, wu, wd = cpu_weights()
+    x = torch.randn(rows, H, generator=torch.Generator().manual_seed(1)).bfloat16()
+    passes = 0
     with torch.inference_mode():
-        for _ in range(repeats):
-            t0 = time.perf_counter()
+        ops_oracle.gated_mlp(x, wg, wu, wd)
+        t0 = time.perf_counter()
+        while True:
             ops_oracle.gated_mlp(x, wg, wu, wd)
-            best = min(best, time.perf_counter() - t0)
-    return rows / best, best
+            passes += 1
+            elapsed = time.perf_counter() - t0
+            if elapsed >= target_seconds or passes >= 10000:
+                break
+    return rows * passes / elapsed, elapsed, passes
 
 
 def cpu_weights():
@@ -176,21 +178,25 @@ def workload_config(n_gpus: int) -> dict:
             "parallelism": f"tp{n_gpus}", "l2": "inputs larger than L2 (weights 352 MB + activations 604 MB per step)"}
 
 
-def comm_plan(args, world: int) -> dict:
+def comm_plan(args, world: int, sms: int | None = None, multicast: bool | None = None) -> dict:
     """How the reduction and the GEMMs share the GPU at N > 1 (flags override the defaults): the
-    reduction inside the NVLink switch on 16 CTAs, on 8 SMs that the GEMMs leave free."""
+    reduction inside the NVLink switch on 16 CTAs, on 8 SMs that the GEMMs leave free.
+    ``sms`` / ``multicast`` default to what the current device reports."""
     if world == 1:
         return {"comm": None, "comm_ctas": 0, "gemm_ctas": 0, "exclusive_sms": False}
-    import torch
-
     kind = args.comm
     if kind == "auto":
-        from dynaflow_b200.comm import multicast_supported
+        if multicast is None:
+            from dynaflow_b200.comm import multicast_supported
 
-        kind = "multicast" if multicast_supported() else "peer"
+            multicast = multicast_supported()
+        kind = "multicast" if multicast else "peer"
     comm_ctas = args.comm_ctas if args.comm_ctas > 0 else (16 if kind == "multicast" else 32)
     exclusive = not args.shared_sms
-    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    if sms is None:
+        import torch
+
+        sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
     gemm_ctas = args.gemm_ctas if args.gemm_ctas >= 0 else (sms - (comm_ctas + 1) // 2 if exclusive else 0)
     return {"comm": kind, "comm_ctas": comm_ctas, "gemm_ctas": gemm_ctas, "exclusive_sms": exclusive}
 
@@ -354,13 +360,11 @@ def run_ours(args) -> None:
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
-        _, probe_s = cpu_port_rate(32)
-        rows = int(max(32, min(2048, 12.0 / (probe_s / 32))) // 32 * 32)
-        rate, secs = cpu_port_rate(rows)
+        rate, secs, passes = cpu_port_sample(12.0, 2048)
         import torch as _t
 
         cpu = {"value": rate, "unit": "tokens/s", "cores": _t.get_num_threads(), "kind": "port",
-               "sample": f"{rows} of {ROWS} rows, one pass of the oracle's gated MLP in {secs:.1f} s (bf16, torch CPU)"}
+               "sample": f"2048 of {ROWS} rows, {passes} passes of the oracle's gated MLP in {secs:.1f} s (bf16, torch CPU)"}
 
     sweep = None
     if world == 1 and not args.no_sweep:
