@@ -31,10 +31,13 @@ def checks(comm, rank: int, world: int, dev: torch.device) -> None:
         ops.check_status()
         rel = ((got.cpu().float() - want.float()).abs().max() / want.float().abs().max()).item()
         assert rel <= 2e-2, f"rank {rank} call {call}: multicast all-reduce rel err {rel}"
-        # the switch does not round to nearest-even: about a fifth of the elements sit one bf16 step
-        # from the rounded fp32 sum (measured with two ranks), none further
-        assert torch.allclose(got.cpu().float(), want.float(), rtol=2.0 ** -6, atol=1e-4 * want.float().abs().max().item()), \
-            f"rank {rank} call {call}: an element is more than two bf16 steps from the fp32 sum"
+        if world == 2:
+            # the switch does not round to nearest-even: with two ranks about a fifth of the elements sit
+            # one bf16 step from the rounded fp32 sum, none further (with more ranks only the 2e-2 bound
+            # above is asserted: the switch's order of summation is not specified)
+            assert torch.allclose(got.cpu().float(), want.float(), rtol=2.0 ** -6,
+                                  atol=1e-4 * want.float().abs().max().item()), \
+                f"rank {rank} call {call}: an element is more than two bf16 steps from the fp32 sum"
         digest = got.view(torch.int16).to(torch.int64).sum().reshape(1)
         all_digests = [torch.zeros_like(digest) for _ in range(world)]
         dist.all_gather(all_digests, digest)
