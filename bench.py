@@ -604,6 +604,9 @@ def run_moe(args) -> None:
             "flops_per_step": flops, "tflops_per_gpu": flops / world / (ms * 1e-3) / 1e12,
             "frac_of_tensor_peak": flops / world / (ms * 1e-3) / 1e12 / float(peaks["bf16_tflops"]),
             "peak_source": f"{kind} cuBLAS bf16 burst", "steps": reps, "data": "synthetic"}
+    # load balance of the first layer's routing (ids of all tokens, two experts each)
+    counts = torch.bincount(stack[0].ids[0].flatten().to(torch.int64), minlength=experts).double()
+    line["tokens_per_expert_max_over_mean"] = float((counts.max() / counts.mean()).item())
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
