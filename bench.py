@@ -224,8 +224,18 @@ def run_ours(args) -> None:
     if world > 1:
         from dynaflow_b200.comm import MulticastComm, PeerComm, set_exclusive_sms
 
-        comm_cls = MulticastComm if plan["comm"] == "multicast" else PeerComm
-        comm = comm_cls(rank, world, ROWS // MICRO_BATCHES, H, slots=MICRO_BATCHES, n_ctas=plan["comm_ctas"], device=dev)
+        if plan["comm"] == "multicast":
+            try:
+                comm = MulticastComm(rank, world, ROWS // MICRO_BATCHES, H, slots=MICRO_BATCHES,
+                                     n_ctas=plan["comm_ctas"], device=dev)
+            except Exception as exc:  # noqa: BLE001 -- e.g. a driver without fabric support: same answer on every rank
+                if args.comm == "multicast":
+                    raise
+                print(f"[bench] no multicast mapping ({exc}); using the peer-memory reduction", file=sys.stderr)
+                args.comm = "peer"
+                plan = comm_plan(args, world)
+        if comm is None:
+            comm = PeerComm(rank, world, ROWS // MICRO_BATCHES, H, slots=MICRO_BATCHES, n_ctas=plan["comm_ctas"], device=dev)
         set_exclusive_sms(plan["exclusive_sms"])
     layer = TensorParallelGatedMLP(H, I, rank=rank, world=world, max_rows=ROWS // MICRO_BATCHES,
                                    micro_batches=MICRO_BATCHES, seed=0, device=dev, comm=comm)
@@ -480,9 +490,20 @@ def run_decoder(args) -> None:
         from dynaflow_b200.comm import set_exclusive_sms
 
         set_exclusive_sms(plan["exclusive_sms"])
-    dec = TensorParallelDecoder(shape, rank=rank, world=world, max_rows=batch * seq // MICRO_BATCHES,
-                                micro_batches=MICRO_BATCHES, seed=0, device=dev, n_ctas=plan["comm_ctas"],
-                                multicast=plan["comm"] == "multicast", gemm_max_ctas=plan["gemm_ctas"])
+    def build_decoder(p):
+        return TensorParallelDecoder(shape, rank=rank, world=world, max_rows=batch * seq // MICRO_BATCHES,
+                                     micro_batches=MICRO_BATCHES, seed=0, device=dev, n_ctas=p["comm_ctas"],
+                                     multicast=p["comm"] == "multicast", gemm_max_ctas=p["gemm_ctas"])
+
+    try:
+        dec = build_decoder(plan)
+    except Exception as exc:  # noqa: BLE001 -- no multicast mapping: the peer-memory reduction instead
+        if plan["comm"] != "multicast" or args.comm == "multicast":
+            raise
+        print(f"[bench] no multicast mapping ({exc}); using the peer-memory reduction", file=sys.stderr)
+        args.comm = "peer"
+        plan = comm_plan(args, world)
+        dec = build_decoder(plan)
     ids = torch.randint(0, shape.vocab, (batch, seq), generator=torch.Generator().manual_seed(1)).to(dev)
 
     def timed(**kw):
