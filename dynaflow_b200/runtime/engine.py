@@ -45,6 +45,8 @@ from .env import ExecutionEnvironment, set_op_handle
 
 # step kinds of the lowered top-level program
 _PLACEHOLDER, _GET_ATTR, _CALL_FUNCTION, _CALL_METHOD, _CALL_MODULE, _OUTPUT = range(6)
+# placeholder kinds: not one / static-shape value (weights) / tensor split by rows / symbolic row count
+_PH_NONE, _PH_STATIC, _PH_ROWS, _PH_SYMINT = range(4)
 _KIND = {"placeholder": _PLACEHOLDER, "get_attr": _GET_ATTR, "call_function": _CALL_FUNCTION,
          "call_method": _CALL_METHOD, "call_module": _CALL_MODULE, "output": _OUTPUT}
 
@@ -76,7 +78,7 @@ def _current_stream_id() -> int:
 
 
 class _Step:
-    __slots__ = ("kind", "node", "target", "placeholder_idx")
+    __slots__ = ("kind", "node", "target", "placeholder_idx", "placeholder_kind")
 
     def __init__(self, node: torch.fx.Node, placeholder_idx: int) -> None:
         if node.op not in _KIND:
@@ -85,6 +87,16 @@ class _Step:
         self.node = node
         self.target = node.target
         self.placeholder_idx = placeholder_idx
+        # what a placeholder is, decided once from its traced example value (a decoder's weights are
+        # placeholders too: hundreds of them per forward and nano-batch)
+        self.placeholder_kind = _PH_NONE
+        if node.op == "placeholder":
+            example = node.meta.get("example_value", None)
+            if isinstance(example, torch.Tensor):
+                dynamic = example.dim() > 0 and isinstance(example.shape[0], torch.SymInt)
+                self.placeholder_kind = _PH_ROWS if dynamic else _PH_STATIC
+            elif isinstance(example, torch.SymInt):
+                self.placeholder_kind = _PH_SYMINT
 
 
 class DynaFlowEngine:
@@ -129,12 +141,10 @@ class DynaFlowEngine:
     def _bind_placeholder(self, step: _Step, batch_idx: int, args: tuple, env: ExecutionEnvironment,
                           cfg: SplitConfig) -> None:
         node, idx = step.node, step.placeholder_idx
-        example = node.meta.get("example_value", None)
-        if isinstance(example, torch.Tensor):
-            dynamic = example.dim() > 0 and isinstance(example.shape[0], torch.SymInt)
-            if not dynamic:
-                env.put(batch_idx, node, args[idx])  # weights and other static-shape inputs
-                return
+        kind = step.placeholder_kind
+        if kind == _PH_STATIC:
+            env.put(batch_idx, node, args[idx])  # weights and other static-shape inputs
+        elif kind == _PH_ROWS:
             start, stop = cfg.split_indices[batch_idx], cfg.split_indices[batch_idx + 1]
             if cfg.use_cudagraph:
                 buf = self.input_buffers[batch_idx].get(idx)
@@ -143,13 +153,13 @@ class DynaFlowEngine:
                 env.put(batch_idx, node, buf[:cfg.num_tokens_padded[batch_idx]])
             else:
                 env.put(batch_idx, node, args[idx][start:stop])
-        elif isinstance(example, torch.SymInt):
+        elif kind == _PH_SYMINT:
             if args[idx] == sum(cfg.num_tokens_padded):
                 env.put(batch_idx, node, cfg.num_tokens_padded[batch_idx])
             else:
                 env.put(batch_idx, node, args[idx])
         else:
-            raise ValueError(f"Invalid example value type: {type(example)}")
+            raise ValueError(f"Invalid example value type: {type(node.meta.get('example_value', None))}")
 
     def _run_simple_step(self, step: _Step, batch_idx: int, args: tuple, env: ExecutionEnvironment,
                          cfg: SplitConfig) -> None:

@@ -110,3 +110,98 @@ def test_get_split_config_agrees_with_live_reference():
         pol = NanoFlowScheduler(make_config(capture_sizes=c["sizes"], cudagraph=True, min_nano_split_tokens=c["min_tokens"]))
         got = pol.get_split_config(InputInfo(len(c["num_tokens"]), c["num_tokens"], sum(c["num_tokens"])), c["cg"])
         assert dataclasses.asdict(got) == want, c
+
+
+_OVERHEAD_CHILD = textwrap.dedent("""
+    import contextlib, importlib.util, io, json, sys, time
+    import torch
+    which = sys.argv[1]
+    sys.path.insert(0, {root!r}); sys.path.insert(0, {root!r} + "/tests")
+    from oracle import llama_oracle
+    torch.set_num_threads(1)
+    shape = llama_oracle.LlamaShape(hidden=32, intermediate=64, heads=2, kv_heads=2, head_dim=16, layers=16, vocab=64)
+    model = llama_oracle.build(shape)
+    ids = llama_oracle.make_ids(4, 8, shape.vocab)
+    cuts = [0, 2, 4]
+    if which == "reference":
+        # the reference package itself, with inert stand-ins for the CUDA events / streams it creates
+        class _E:
+            def __init__(self, *a, **k): pass
+            def record(self, *a, **k): pass
+            def wait(self, *a, **k): pass
+            def synchronize(self): pass
+        class _S:
+            def __init__(self, *a, **k): pass
+        torch.cuda.Event, torch.cuda.Stream = _E, _S
+        torch.cuda.stream = lambda s: contextlib.nullcontext()
+        sys.path.insert(0, {ref!r})
+        import dynaflow.config as C, dynaflow.interface as I, dynaflow.matching as M, dynaflow.manager as G
+        spec = importlib.util.spec_from_file_location("_p", {ref!r} + "/examples/ae/scheduler/hf/nanoflow.py")
+        hf = importlib.util.module_from_spec(spec); spec.loader.exec_module(hf)
+        class Policy(hf.NanoFlowScheduler):
+            def get_split_rules(self):
+                return [M.MatchingRule(condition=M.Op(pattern=r"scaled_dot_product_attention"))]
+            def get_tag_rules(self):
+                return {{M.MatchingRule(condition=M.Op(pattern=r"scaled_dot_product_attention")): {{"network"}}}}
+        cfg = C.DynaFlowConfig("x:y", 2, C.InductorConfig(False), C.CUDAGraphConfig(False, [64]), {{"min_nano_split_tokens": 1}})
+        manager, policy = G.DynaFlowManager(), Policy(cfg)
+        def backend(gm, example_inputs):
+            manager.initialize(graph_module=gm, config=cfg, scheduler=policy, example_inputs=list(example_inputs))
+            return manager.get_callable()
+        split = lambda: I.SplitConfig(2, [2, 2], cuts, [2, 2], [2, 2], cuts, False, False)
+        n_ops = lambda: 2 * len(manager.engine.module_name_to_node)
+    else:
+        from helpers import cut_policy, make_config, two_way
+        from dynaflow_b200.manager import DynaFlowManager
+        cfg = make_config()
+        manager, policy = DynaFlowManager(), cut_policy(r"scaled_dot_product_attention", "network", cfg)
+        def backend(gm, example_inputs):
+            manager.initialize(graph_module=gm, config=cfg, scheduler=policy, example_inputs=list(example_inputs))
+            return manager.get_callable()
+        split = lambda: two_way(cuts)
+        n_ops = lambda: 2 * len(manager.engine.module_name_to_node)
+    torch._dynamo.reset()
+    torch._dynamo.mark_dynamic(ids, 0)
+    compiled = torch.compile(model, backend=backend, fullgraph=True)
+    def forward():
+        manager.override_split_config(split())
+        with torch.inference_mode(), contextlib.redirect_stdout(io.StringIO()):
+            return compiled(ids)
+    for _ in range(5):
+        out = forward()
+    best = float("inf")
+    for _ in range(5):
+        t0 = time.perf_counter()
+        for _ in range(20):
+            forward()
+        best = min(best, (time.perf_counter() - t0) / 20)
+    with torch.inference_mode():
+        t0 = time.perf_counter()
+        for _ in range(20):
+            want = model(ids)
+        eager = (time.perf_counter() - t0) / 20
+    ok = bool((out - want).abs().max() / want.abs().max() <= 1e-5)
+    print(json.dumps({{"which": which, "ms_per_forward": best * 1e3, "ms_eager_unsplit": eager * 1e3, "dispatches": n_ops(), "ok": ok}}))
+""")
+
+
+def test_host_dispatch_overhead_vs_reference(capsys):
+    """Host cost of one split forward (2 nano-batches, 16-layer toy decoder cut at attention: 66 operator
+    dispatches, CPU tensors small enough that dispatch dominates): this package's synchronous dispatcher
+    against the reference's engine/policy coroutine pair on a per-forward event loop
+    (``dynaflow/manager.py:161-261``, ``runtime/engine.py:222-424``), same policy logic, same machine."""
+    import json
+
+    results = {}
+    for which in ("reference", "ours"):
+        code = _OVERHEAD_CHILD.format(root=ROOT, ref=REFERENCE)
+        proc = subprocess.run([sys.executable, "-c", code, which], capture_output=True, text=True, timeout=900)
+        assert proc.returncode == 0, proc.stderr[-3000:]
+        results[which] = json.loads(proc.stdout.splitlines()[-1])
+        assert results[which]["ok"]
+    ref, ours = results["reference"], results["ours"]
+    assert ref["dispatches"] == ours["dispatches"]
+    with capsys.disabled():
+        print(f"\nhost dispatch, {ours['dispatches']} dispatches per forward: reference {ref['ms_per_forward']:.3f} ms, "
+              f"dynaflow_b200 {ours['ms_per_forward']:.3f} ms (unsplit eager model {ours['ms_eager_unsplit']:.3f} ms)")
+    assert ours["ms_per_forward"] < ref["ms_per_forward"]
