@@ -45,6 +45,7 @@ SIGNATURES: dict[str, tuple] = {
     "df_status_clear": (_i, [_vp, _vp]),
     "df_gemm_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
     "df_gateup_silu_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp]),
+    "df_set_launch_option": (_i, [_i, _i]),
     "df_gemm_splitk_workspace_bytes": (_sz, []),
     "df_gemm_bf16_ws": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp, _vp]),
     "df_gateup_silu_bf16_ws": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp, _vp]),
@@ -72,6 +73,7 @@ SIGNATURES: dict[str, tuple] = {
     "df_allreduce_multicast_bf16": (_i, [_rank_p, _vp, _i, _i, _i, _i, _i, _vp, _f, _i, _vp, _vp]),
     "df_add_rmsnorm_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _i, _i, _vp]),
     "df_allreduce_emulated_bf16": (_i, [_rank_p, _i, _i, _i, _i, _vp, _f, _i, _i, _vp, _vp]),
+    "df_attention_prefill_bf16": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp, _vp]),
     "df_mlp_gated_bf16_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
 }
 

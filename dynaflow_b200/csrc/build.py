@@ -1,6 +1,11 @@
 """Builds the C-ABI shared library in-tree with nvcc for sm_100a.
 
-    python -m dynaflow_b200.csrc.build [--force]
+    python -m dynaflow_b200.csrc.build [--force] [--dev-knobs]
+
+``--dev-knobs`` compiles with ``-DDF_DEV_KNOBS``: the GEMM launches then read their tuning
+integers (tile grouping, pipeline depth, CTA pairs, and switches that skip the operand copies or
+the output stores for timing diagnostics, which make the results invalid) from ``DF_GEMM_*``
+environment variables. The default build has none of them.
 
 The result is ``dynaflow_b200/lib/libdynaflow_b200.so``; it links against the
 CUDA runtime only (the one driver entry point it needs is resolved at run time).
@@ -42,7 +47,7 @@ def find_nvcc() -> str:
     return nvcc
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, dev_knobs: bool = False) -> str:
     """Compiles the library if it is missing or older than its sources; returns its path."""
     if not force and os.path.exists(LIB_PATH) and os.path.getmtime(LIB_PATH) >= _newest_input():
         return LIB_PATH
@@ -50,6 +55,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     cmd = [find_nvcc(), *NVCC_FLAGS]
     if verbose:
         cmd += ["-Xptxas", "-v"]
+    if dev_knobs:
+        cmd += ["-DDF_DEV_KNOBS"]
     cmd += ["-o", LIB_PATH, *sources()]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
@@ -60,4 +67,5 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv or "--dev-knobs" in sys.argv, verbose="-v" in sys.argv,
+                dev_knobs="--dev-knobs" in sys.argv))

@@ -114,12 +114,22 @@ __device__ __forceinline__ bool peer_barrier(const RankView& me, int world, int 
     const uint32_t* mine = me.flags[me.rank] + slot + t;
     uint32_t spins = 0;
     // flags only grow; compare as a signed distance so that wrap-around is harmless
-    while (static_cast<int32_t>(ld_acquire_sys(mine) - value) < 0) {
+    uint32_t seen;
+    while (static_cast<int32_t>((seen = ld_acquire_sys(mine)) - value) < 0) {
       if ((++spins & 0xffu) == 0u && globaltimer_ns() > t_end) {
         *s_abort = 1u;
         report(status, 2u /*DF_ERR_PEER*/, WHERE_FLAG + phase, static_cast<unsigned>(t));
+        seen = value;
         break;
       }
+    }
+    // In step, a peer can never be ahead of the value waited for: it reaches its next flag of
+    // this phase only through the other phase's barrier, which needs this rank's next signal.
+    // A flag that is ahead therefore belongs to a peer that gave up on an earlier barrier and
+    // went on alone; its contribution to this launch is missing, so this rank reports it too.
+    if (seen != value) {
+      *s_abort = 1u;
+      report(status, 2u /*DF_ERR_PEER*/, WHERE_FLAG + phase, static_cast<unsigned>(t));
     }
   }
   __syncthreads();

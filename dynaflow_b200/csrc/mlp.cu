@@ -31,6 +31,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -76,6 +77,12 @@ static inline int stages_for(int a_rows) {
 enum : int { MODE_PLAIN = 0, MODE_GATEUP = 1, MODE_FUSED = 2 };  // FUSED: gate/up tiles then down tiles, one launch
 enum : unsigned { WHERE_PRODUCER = 1, WHERE_MMA_FULL = 2, WHERE_MMA_TMEM = 3, WHERE_EPILOGUE = 4 };
 
+#ifdef DF_DEV_KNOBS
+constexpr bool kDevKnobs = true;
+#else
+constexpr bool kDevKnobs = false;
+#endif
+
 constexpr int kMaxChunks = 64;
 
 // MODE_FUSED only: the tile index space is a sequence of chunks, each a group of row panels in
@@ -111,7 +118,7 @@ struct GemmParams {
   // Row count known only on the device (tokens routed to an expert): if non-NULL, the kernel
   // processes min(*m_dev, M) rows and M is the capacity the tensor maps were built for.
   const int* m_dev;
-  int debug;  // development only: bit 0 = producer skips the copies, bit 1 = epilogue skips the stores
+  int debug;  // DF_DEV_KNOBS builds only: bit 0 = producer skips the copies, bit 1 = epilogue skips the stores
   // 1-CTA tiles: a_rows = rows of A a stage has room for (a multiple of 16, at most 128), a_tx =
   // bytes one copy of A delivers (its box has exactly the launch's rows when there are fewer than
   // 128, so that no copy runs past the matrix: such rows cost a measured 0.3 us per k-block),
@@ -416,7 +423,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
           }
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
-          if (p.debug & 1) {
+          if (kDevKnobs && (p.debug & 1)) {
             if (cta_rank == 0) mbar_arrive(&full[stage]);
           } else if (CTAS == 2) {
             // this CTA's half of B: gate rows on the leader, up rows on its peer (GATEUP);
@@ -487,11 +494,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             }
           }
           if (CTAS == 2) {
-            if (p.debug & 4) {
-              umma_commit_2cta_mask(&empty[stage], 3);
-            } else {
-              umma_commit_2cta(&empty[stage]);  // frees the stage in both CTAs
-            }
+            umma_commit_2cta(&empty[stage]);  // frees the stage in both CTAs
           } else {
             umma_commit(&empty[stage]);
           }
@@ -502,11 +505,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         }
         if (ok) {
           if (CTAS == 2) {
-            if (p.debug & 4) {
-              umma_commit_2cta_mask(&tfull[acc], 3);
-            } else {
-              umma_commit_2cta(&tfull[acc]);
-            }
+            umma_commit_2cta(&tfull[acc]);
           } else {
             umma_commit(&tfull[acc]);
           }
@@ -539,7 +538,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
       tc_fence_after();
       const uint32_t t_acc = tmem_base + static_cast<uint32_t>(acc * ACC_COLS) + (static_cast<uint32_t>(q * 32) << 16);
       __nv_bfloat16* crow = c_base + static_cast<size_t>(row) * c_ld;
-      const bool row_ok = row < rows_m && !(p.debug & 2);
+      const bool row_ok = row < rows_m && !(kDevKnobs && (p.debug & 2));
 
       if (SKINNY) {
         // this thread owns weight row i of both halves: output column n0 + i (gate/up), or the
@@ -570,7 +569,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             }
             continue;
           }
-          if (p.debug & 2) continue;
+          if (kDevKnobs && (p.debug & 2)) continue;
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int r = c * 16 + j;
@@ -727,7 +726,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         epilogue_bar_sync();
         if (*dl.abort) break;
         const int row = sk_mblk[k] * Cfg::kTileM + tid;
-        if (row >= rows_m || (p.debug & 2)) continue;
+        if (row >= rows_m || (kDevKnobs && (p.debug & 2))) continue;
         const int g_lo = s_idx * GROUPS / S, g_hi = (s_idx + 1) * GROUPS / S;
         // partial o of the tile: contributor first + o; o = 0 started the tile (slot 1), the others slot 0
         const float* base = p.sk_partials + static_cast<size_t>(2 * first) * (ACC_COLS * BM) + tid;
@@ -875,7 +874,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
               a1[u] += v1[u];
             }
           }
-          if (p.debug & 2) continue;
+          if (kDevKnobs && (p.debug & 2)) continue;
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int e = e0 + u * 128;
@@ -942,13 +941,27 @@ static bool make_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uin
   return true;
 }
 
-// Development knob: integer taken from the environment on every launch (cheap: getenv).
+// Launch-form options (df_set_launch_option): which of the bit-different but equally valid
+// forms of a launch is chosen. Process-wide, read at every launch.
+static std::atomic<int> g_launch_option[DF_OPT_COUNT_] = {{1}, {1}, {1}};
+static int launch_option(int opt) { return g_launch_option[opt].load(std::memory_order_relaxed); }
+
+// Development knobs exist only in builds with -DDF_DEV_KNOBS (integers taken from the
+// environment on every launch, among them switches that skip the copies or the stores and so
+// produce invalid results, for timing diagnostics). The shipped library compiles them to
+// their defaults.
+#ifdef DF_DEV_KNOBS
+constexpr bool kDevKnobsHost = true;
 static int tuning_int(const char* name, int fallback) {
   const char* v = std::getenv(name);
   if (v == nullptr || *v == '\0') return fallback;
   const int x = std::atoi(v);
   return x >= 0 ? x : fallback;
 }
+#else
+constexpr bool kDevKnobsHost = false;
+static inline int tuning_int(const char*, int fallback) { return fallback; }
+#endif
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -1020,7 +1033,7 @@ static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b0, con
   p.sk_per = 0;
   p.sk_partials = nullptr;
   p.sk_counters = nullptr;
-  if (CTAS == 1 && sk_ws != nullptr && p.m_dev == nullptr && tuning_int("DF_GEMM_STREAMK", 1) != 0) {
+  if (CTAS == 1 && sk_ws != nullptr && p.m_dev == nullptr && launch_option(DF_OPT_STREAM_K) != 0) {
     const int waves = (p.num_tiles + units - 1) / units;
     const double eff = static_cast<double>(p.num_tiles) / (static_cast<double>(waves) * units);
     const long long total = static_cast<long long>(p.num_tiles) * p.num_kb;
@@ -1063,12 +1076,23 @@ static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b0, con
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr;
-  attr.id = cudaLaunchAttributeClusterDimension;
-  attr.val.clusterDim.x = CTAS;
-  attr.val.clusterDim.y = 1;
-  attr.val.clusterDim.z = 1;
-  cfg.attrs = &attr;
-  cfg.numAttrs = 1;
+  if (CTAS == 2) {
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = CTAS;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+  } else if (p.sk_per > 0) {
+    // In the stream-K finish every contributor of a tile waits for all the others, which is only
+    // free of cycles if all CTAs of the grid are resident at once. A cooperative launch makes the
+    // runtime guarantee exactly that, whatever else occupies SMs when the grid starts (a second
+    // stream-K launch on another stream, the reduction kernel, a graph replay).
+    attr.id = cudaLaunchAttributeCooperative;
+    attr.val.cooperative = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+  }
   cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b0, tm_b1, tm_a, tm_b0, p);
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
@@ -1200,8 +1224,8 @@ static int launch_gemm(const void* a, const void* b0, const void* b1, void* c, i
   int sms = df_sm_count();
   if (sms <= 0) return fail(DF_ECUDA, "no CUDA device");
 
-  // At most 64 rows: the operand-swapped form with a smaller A stage and a deeper pipeline.
-  const bool skinny = M <= tuning_int("DF_GEMM_SKINNY_ROWS", 128) && M <= BM && m_dev == nullptr && tuning_int("DF_GEMM_SKINNY", 1) != 0 &&
+  // At most 128 rows: the operand-swapped form with a smaller A stage and a deeper pipeline.
+  const bool skinny = M <= tuning_int("DF_GEMM_SKINNY_ROWS", 128) && M <= BM && m_dev == nullptr && launch_option(DF_OPT_OPERAND_SWAP) != 0 &&
                       tuning_int("DF_GEMM_CTAS", 1) != 2;
   const int a_rows = skinny ? ((M + 15) / 16) * 16 : BM;
   const int a_box_rows = M < BM ? M : BM;  // a launch of fewer than 128 rows never copies past its last row
@@ -1272,6 +1296,12 @@ int df_gateup_silu_bf16_ws(const void* x, const void* w_gate, const void* w_up, 
                                           splitk_ws_bytes, dev_status, stream);
 }
 
+int df_set_launch_option(int option, int value) {
+  if (option < 0 || option >= DF_OPT_COUNT_) return df::fail(DF_EINVAL, "unknown launch option %d", option);
+  df::g_launch_option[option].store(value != 0 ? 1 : 0, std::memory_order_relaxed);
+  return DF_OK;
+}
+
 size_t df_gemm_splitk_workspace_bytes(void) {
   const int sms = df_sm_count();
   return df::splitk_workspace_bytes_for(sms > 0 ? sms : 148);
@@ -1304,7 +1334,7 @@ int df_mlp_gated_bf16(const void* x, const void* w_gate, const void* w_up, const
   const long long up_tiles = static_cast<long long>((M + 127) / 128) * ((I + 127) / 128);
   const long long down_tiles = static_cast<long long>((M + 127) / 128) * ((H + 127) / 128);
   const bool down_wants_stream_k = down_tiles <= units && down_tiles * 10 < static_cast<long long>(units) * 6;
-  if (sms > 0 && up_tiles > units && !down_wants_stream_k && df::tuning_int("DF_MLP_FUSED", 1) != 0 && (H % 8) == 0 && (I % 8) == 0 &&
+  if (sms > 0 && up_tiles > units && !down_wants_stream_k && df::launch_option(DF_OPT_MLP_ONE_LAUNCH) != 0 && (H % 8) == 0 && (I % 8) == 0 &&
       x != nullptr && w_gate != nullptr && w_up != nullptr && w_down != nullptr && out != nullptr &&
       dev_status != nullptr && df::aligned16(x) && df::aligned16(w_gate) && df::aligned16(w_up) &&
       df::aligned16(w_down) && df::aligned16(out))

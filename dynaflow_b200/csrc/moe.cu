@@ -97,10 +97,10 @@ __global__ void select_rows_kernel(const int* __restrict__ ids, int T, int exper
   if (threadIdx.x == 0) *count = base;
 }
 
-// out[k, :] = x[rows[k], :] for k < *count; one warp per row, 16-byte vectors.
+// out[k, :] = x[rows[k], :] for k < min(*count, capacity); one warp per row, 16-byte vectors.
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ rows,
-                                   const int* __restrict__ count, int H, __nv_bfloat16* __restrict__ out) {
-  const int n = *count;
+                                   const int* __restrict__ count, int capacity, int H, __nv_bfloat16* __restrict__ out) {
+  const int n = min(*count, capacity);
   const int warps = (gridDim.x * blockDim.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int nvec = H >> 3;
@@ -183,7 +183,7 @@ int df_moe_gather_rows(const void* x, const int* rows, const int* count_dev, int
     return df::fail(DF_EINVAL, "NULL pointer argument");
   if (capacity <= 0 || H <= 0 || (H % 8) != 0) return df::fail(DF_EINVAL, "capacity must be positive, H a multiple of 8");
   df::gather_rows_kernel<<<df::grid_for_rows(capacity), df::kMoeThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), rows, count_dev, H, static_cast<__nv_bfloat16*>(out));
+      static_cast<const __nv_bfloat16*>(x), rows, count_dev, capacity, H, static_cast<__nv_bfloat16*>(out));
   return df::check_launch("gather_rows");
 }
 

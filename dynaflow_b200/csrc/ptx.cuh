@@ -227,14 +227,6 @@ __device__ __forceinline__ void umma_commit_2cta(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(a1) : "memory");
 }
 
-// Broadcast form of the same commit: one instruction, one arrival in each CTA of the mask.
-__device__ __forceinline__ void umma_commit_2cta_mask(uint64_t* bar, uint16_t cta_mask) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::
-                   "r"(smem_u32(bar)),
-               "h"(cta_mask)
-               : "memory");
-}
-
 // 32 lanes x 32 consecutive fp32 columns: thread i of the warp receives lane
 // (base lane + i), columns [col, col + 32).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {

@@ -17,7 +17,7 @@ from . import _native
 from ._native import df_status_t
 
 DEVICE_ERRORS = {1: "DF_ERR_TIMEOUT", 2: "DF_ERR_PEER"}
-_WHERE = {1: "tma-producer", 2: "mma(full)", 3: "mma(tmem-empty)", 4: "epilogue", 5: "h-ready", 16: "peer-flag"}
+_WHERE = {1: "tma-producer", 2: "mma(full)", 3: "mma(tmem-empty)", 4: "epilogue", 5: "h-ready", 16: "peer-flag", 32: "attention-producer", 33: "attention-mma", 34: "attention-softmax"}
 
 
 class DeviceStatusError(RuntimeError):
@@ -68,6 +68,16 @@ def check_status(device=None) -> None:
 
 def set_timeout_ms(ms: int) -> None:
     rc = _native.load().df_set_timeout_ms(int(ms))
+    if rc != 0:
+        raise ValueError(_native.last_error())
+
+
+LAUNCH_OPTIONS = {"stream_k": 0, "mlp_one_launch": 1, "operand_swap": 2}
+
+
+def set_launch_option(name: str, on: bool) -> None:
+    """Switches one of the equally valid launch forms on or off (``df_set_launch_option``)."""
+    rc = _native.load().df_set_launch_option(LAUNCH_OPTIONS[name], int(bool(on)))
     if rc != 0:
         raise ValueError(_native.last_error())
 
@@ -186,6 +196,36 @@ def gated_mlp(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down:
                                           out.data_ptr(), workspace.data_ptr(), M, H, I, max_ctas, st.data_ptr(),
                                           _stream_ptr(x))
     _check(rc, "df_mlp_gated_bf16")
+    return out
+
+
+def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, *, batch: int, seq_len: int,
+                      cu_seqlens: torch.Tensor | None = None, scale: float | None = None, max_ctas: int = 0) -> torch.Tensor:
+    """Causal grouped-query attention of a prefill nano-batch. ``q [T, Hq*128]``, ``k, v [T, Hkv*128]``,
+    ``out [T, Hq*128]``: 2-D bf16 views with unit inner stride (column ranges of a fused qkv
+    activation are fine). The ``T`` rows are ``batch`` sequences back to back, each ``seq_len``
+    long, or starting at ``cu_seqlens[b]`` (int32 on the device, ``batch + 1`` entries; ``seq_len``
+    is then the longest length)."""
+    for name, t in (("q", q), ("k", k), ("v", v), ("out", out)):
+        _require_bf16_2d(name, t)
+    T = q.shape[0]
+    hd = 128
+    if q.shape[1] % hd or k.shape[1] % hd or tuple(k.shape) != tuple(v.shape) or tuple(out.shape) != tuple(q.shape) \
+            or k.shape[0] != T:
+        raise ValueError("expected q/out [T, Hq*128] and k/v [T, Hkv*128]")
+    if T == 0:
+        return out
+    if cu_seqlens is not None and (cu_seqlens.dtype != torch.int32 or not cu_seqlens.is_cuda
+                                   or cu_seqlens.numel() != batch + 1):
+        raise ValueError("cu_seqlens must be an int32 device tensor of batch + 1 entries")
+    _dev_index(q)
+    st = status_block(q.device)
+    rc = _native.load().df_attention_prefill_bf16(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), T, batch, seq_len,
+        cu_seqlens.data_ptr() if cu_seqlens is not None else None, q.shape[1] // hd, k.shape[1] // hd, hd,
+        q.stride(0), k.stride(0), v.stride(0), out.stride(0), float(scale if scale is not None else hd ** -0.5),
+        max_ctas, st.data_ptr(), _stream_ptr(q))
+    _check(rc, "df_attention_prefill_bf16")
     return out
 
 

@@ -120,6 +120,18 @@ int df_gateup_silu_bf16_ws(const void* x, const void* w_gate, const void* w_up, 
                            int ldx, int ldw, int ldh, int max_ctas, void* splitk_ws, size_t splitk_ws_bytes,
                            df_status_t* dev_status, void* stream);
 
+/* Which of several equally valid forms a launch takes (all on by default). The forms differ in
+ * the order of the fp32 summation, hence possibly in the last bf16 bit, never in validity; tests
+ * switch them off to compare forms with each other. Process-wide; no counterpart in the reference.
+ *   DF_OPT_STREAM_K        stream-K partition of launches with fewer tiles than SMs
+ *   DF_OPT_MLP_ONE_LAUNCH  df_mlp_gated_bf16 as one persistent launch where it applies
+ *   DF_OPT_OPERAND_SWAP    operand-swapped tiles for launches of at most 128 rows */
+#define DF_OPT_STREAM_K 0
+#define DF_OPT_MLP_ONE_LAUNCH 1
+#define DF_OPT_OPERAND_SWAP 2
+#define DF_OPT_COUNT_ 3
+int df_set_launch_option(int option, int value);
+
 /* Bytes of scratch df_mlp_gated_bf16 needs: the bf16 intermediate h[M,I] plus one
  * stream-K workspace. */
 size_t df_mlp_workspace_bytes(int M, int H, int I);
@@ -270,7 +282,8 @@ int df_moe_route_top2(const void* logits, int T, int E, int* ids, float* weights
  * choice), pos[t] = k or -1, *count_dev = how many. rows/slot need T entries, pos T entries. */
 int df_moe_select_rows(const int* ids, int T, int expert, int* rows, int* slot, int* pos, int* count_dev, void* stream);
 
-/* out[k,:] = x[rows[k],:] for k < *count_dev (bf16, H % 8 == 0; out has `capacity` rows). */
+/* out[k,:] = x[rows[k],:] for k < min(*count_dev, capacity) (bf16, H % 8 == 0; out has `capacity` rows,
+ * rows beyond that are not written). */
 int df_moe_gather_rows(const void* x, const int* rows, const int* count_dev, int capacity, int H, void* out,
                        void* stream);
 
@@ -290,6 +303,26 @@ int df_mlp_gated_bf16_rows_on_device(const void* x, const void* w_gate, const vo
  * rotated by positions[t]. Part of the attention subgraph's prologue in a decoder layer. */
 int df_rope_bf16(void* qkv, const int* positions, int T, int heads, int head_dim, int row_stride, float theta,
                  void* stream);
+
+/* ----------------------------------------------------------------- attention
+ *
+ * The attention core of a decoder layer: the subgraph the reference's policies cut out, tag
+ * `attention` and leave to the host model's own kernels, setting the nano-batch's attention
+ * metadata before each call (examples/ae/scheduler/vllm/nanoflow.py:91-94, 231).
+ *
+ * Causal self-attention of a prefill nano-batch, grouped-query: q [total_rows, q_heads * 128],
+ * k and v [total_rows, kv_heads * 128], out [total_rows, q_heads * 128], all bf16 with explicit row
+ * strides in elements (the three inputs may be column ranges of one fused qkv activation).
+ * The rows are `batch` sequences back to back; with cu_seqlens_dev == NULL every sequence has
+ * seq_len rows (total_rows == batch * seq_len), otherwise cu_seqlens_dev[b] (device memory,
+ * batch + 1 ints) is the first row of sequence b and seq_len the longest length. Query head h
+ * reads key/value head h / (q_heads / kv_heads). out = softmax(scale * q k^T + causal mask) v,
+ * scores and sums in fp32, probabilities rounded to bf16 before the second product.
+ * head_dim must be 128. max_ctas <= 0 means one CTA per SM. */
+int df_attention_prefill_bf16(const void* q, const void* k, const void* v, void* out, int total_rows, int batch,
+                              int seq_len, const int* cu_seqlens_dev, int q_heads, int kv_heads, int head_dim,
+                              int ld_q, int ld_k, int ld_v, int ld_out, float scale, int max_ctas,
+                              df_status_t* dev_status, void* stream);
 
 /* Size of the library-owned scratch behind df_mlp_gated_bf16_static: 64 MiB of
  * static device memory, held by every GPU that loads the library until the

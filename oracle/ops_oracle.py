@@ -88,3 +88,30 @@ def moe_layer(x: torch.Tensor, router_logits: torch.Tensor, w_gate: torch.Tensor
         y = gated_mlp(x[rows], w_gate[e], w_up[e], w_down[e])
         out.index_add_(0, rows, y.float() * weights[rows, slot].unsqueeze(-1))
     return out.to(x.dtype)
+
+
+def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seq_lens: list[int],
+                     scale: float | None = None) -> torch.Tensor:
+    """Causal grouped-query self-attention over sequences packed back to back along dim 0.
+    ``q [T, Hq, D]``, ``k, v [T, Hkv, D]`` -> ``[T, Hq, D]``. The attention subgraph of a
+    decoder layer is opaque to the reference (``examples/ae/scheduler/vllm/nanoflow.py:91-94``:
+    whatever kernel the host model calls); the statement here is the one
+    ``torch.nn.functional.scaled_dot_product_attention(is_causal=True)`` documents: scores and
+    softmax in fp32, probabilities rounded to the tensor dtype before the product with ``v``,
+    fp32 accumulation, one final rounding."""
+    T, hq, d = q.shape
+    hkv = k.shape[1]
+    scale = scale if scale is not None else d ** -0.5
+    out = torch.empty_like(q)
+    start = 0
+    for n in seq_lens:
+        qs = q[start:start + n].float().transpose(0, 1)                       # [Hq, n, D]
+        ks = k[start:start + n].float().transpose(0, 1).repeat_interleave(hq // hkv, dim=0)
+        vs = v[start:start + n].float().transpose(0, 1).repeat_interleave(hq // hkv, dim=0)
+        s = (qs @ ks.transpose(1, 2)) * scale
+        s = s.masked_fill(torch.ones(n, n, dtype=torch.bool).triu(1), float("-inf"))
+        p = torch.softmax(s, dim=-1).to(q.dtype).float()
+        out[start:start + n] = (p @ vs).transpose(0, 1).to(q.dtype)
+        start += n
+    assert start == T
+    return out

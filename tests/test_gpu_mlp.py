@@ -99,8 +99,6 @@ def test_micro_batch_split_is_bit_exact_at_full_size(ops):
     wg = (torch.randn(I, H, device="cuda", generator=g) * 0.02).bfloat16()
     wu = (torch.randn(I, H, device="cuda", generator=g) * 0.02).bfloat16()
     wd = (torch.randn(H, I, device="cuda", generator=g) * 0.02).bfloat16()
-    import os
-
     full = ops.gated_mlp(x, wg, wu, wd)
     for cut in (M // 2, 1000):
         parts = torch.cat([ops.gated_mlp(x[:cut].contiguous(), wg, wu, wd), ops.gated_mlp(x[cut:].contiguous(), wg, wu, wd)])
@@ -111,12 +109,12 @@ def test_micro_batch_split_is_bit_exact_at_full_size(ops):
             # stream-K path (partial sums combined in fp32): equal within rounding, and identical
             # again once that path is switched off
             assert rel_err(parts, full.cpu()) <= 1e-2
-            os.environ["DF_GEMM_STREAMK"] = "0"
+            ops.set_launch_option("stream_k", False)
             try:
                 parts = torch.cat([ops.gated_mlp(x[:cut].contiguous(), wg, wu, wd),
                                    ops.gated_mlp(x[cut:].contiguous(), wg, wu, wd)])
             finally:
-                os.environ["DF_GEMM_STREAMK"] = "1"
+                ops.set_launch_option("stream_k", True)
             assert torch.equal(parts, full)
     ops.check_status()
     # scaling the input by 2 scales the gate pre-activation: check linearity of the down projection instead
@@ -134,14 +132,12 @@ def test_micro_batch_split_is_bit_exact_at_full_size(ops):
 
 def test_limited_grid_gives_identical_results(ops):
     x, w, wd = _rand((512, 256), 1.0, 1).cuda(), _rand((1024, 256), 0.05, 2).cuda(), _rand((256, 1024), 0.05, 3).cuda()
-    import os
-
-    os.environ["DF_GEMM_STREAMK"] = "0"   # whole tiles on both sides: the grid size must not change a bit
+    ops.set_launch_option("stream_k", False)   # whole tiles on both sides: the grid size must not change a bit
     try:
         a = ops.gated_mlp(x, w, w, wd)
         b = ops.gated_mlp(x, w, w, wd, max_ctas=7)
     finally:
-        os.environ["DF_GEMM_STREAMK"] = "1"
+        ops.set_launch_option("stream_k", True)
     ops.check_status()
     assert torch.equal(a, b)
     c = ops.gated_mlp(x, w, w, wd, max_ctas=40)   # stream-K may engage: same values within rounding
@@ -179,13 +175,11 @@ def test_small_m_stream_k_path(ops, M, H, I):
     assert rel_err(h1, ops_oracle.silu_mul(g, u)) <= TOL
     assert rel_err(out1, ops_oracle.gated_mlp(x, wg, wu, wd)) <= TOL
     # the plain entry point without a workspace (whole tiles only) agrees within tolerance
-    import os
-
-    os.environ["DF_GEMM_STREAMK"] = "0"
+    ops.set_launch_option("stream_k", False)
     try:
         out3 = ops.gated_mlp(*dev)
     finally:
-        os.environ["DF_GEMM_STREAMK"] = "1"
+        ops.set_launch_option("stream_k", True)
     ops.check_status()
     assert rel_err(out3, out1) <= 1e-2
 
@@ -195,20 +189,18 @@ def test_one_launch_mlp_equals_two_launches(ops, M, H, I):
     """df_mlp_gated_bf16 runs gate/up and down as ONE persistent launch (down tiles wait on
     per-panel counters for their rows of the intermediate). Same tiles, same accumulation
     order: the result must be bit-identical to the two separate launches, every time."""
-    import os
-
     g = torch.Generator(device="cuda").manual_seed(M + I)
     x = torch.randn(M, H, device="cuda", generator=g).bfloat16()
     wg = (torch.randn(I, H, device="cuda", generator=g) * 0.02).bfloat16()
     wu = (torch.randn(I, H, device="cuda", generator=g) * 0.02).bfloat16()
     wd = (torch.randn(H, I, device="cuda", generator=g) * 0.02).bfloat16()
-    os.environ["DF_MLP_FUSED"] = "0"
-    os.environ["DF_GEMM_STREAMK"] = "0"      # whole tiles, as the single launch computes them
+    ops.set_launch_option("mlp_one_launch", False)
+    ops.set_launch_option("stream_k", False)      # whole tiles, as the single launch computes them
     try:
         two = ops.gated_mlp(x, wg, wu, wd)
     finally:
-        os.environ["DF_MLP_FUSED"] = "1"
-        os.environ["DF_GEMM_STREAMK"] = "1"
+        ops.set_launch_option("mlp_one_launch", True)
+        ops.set_launch_option("stream_k", True)
     for _ in range(5):
         one = ops.gated_mlp(x, wg, wu, wd)
         if ((M + 127) // 128) * ((H + 127) // 128) >= 128:   # fewer down tiles take the stream-K path
@@ -227,8 +219,6 @@ def test_decode_rows_operand_swapped_form(ops, M, H, I):
     """Launches of at most 128 rows take the operand-swapped form of the GEMM kernel (weight rows on
     the accumulator lanes, token rows on its columns, stream-K partial sums finished cooperatively).
     Against the oracle, against the regular form, bit-reproducible, and nothing written past row M."""
-    import os
-
     from oracle import ops_oracle
 
     x = _rand((M, H), 1.0, 21)
@@ -247,10 +237,10 @@ def test_decode_rows_operand_swapped_form(ops, M, H, I):
     g = torch.nn.functional.linear(x, wg)
     u = torch.nn.functional.linear(x, wu)
     assert rel_err(h, ops_oracle.silu_mul(g, u)) <= TOL
-    os.environ["DF_GEMM_SKINNY"] = "0"
+    ops.set_launch_option("operand_swap", False)
     try:
         regular = ops.gated_mlp(*dev)
     finally:
-        os.environ["DF_GEMM_SKINNY"] = "1"
+        ops.set_launch_option("operand_swap", True)
     ops.check_status()
     assert rel_err(out, regular) <= 1e-2
