@@ -1,12 +1,13 @@
 """A Llama-style decoder stack on the batch-split, overlapped schedule, tensor parallel.
 
-Everything on the hot path except the attention core runs on this library's kernels: fused
-qkv projection and output projection (``ops.gemm_bf16``), rotary embedding
-(``df_rope_bf16``), the gated MLP (``ops.gated_mlp``), and between the blocks the
-reduce-scatter / residual add / RMSNorm / all-gather kernel on the communication stream
-(single rank: the stand-alone add + RMSNorm kernel). The attention core is PyTorch's
-``scaled_dot_product_attention``: the reference treats attention as an opaque subgraph as
-well (``examples/ae/scheduler/vllm/nanoflow.py:91-94``).
+Everything on the hot path runs on this library's kernels: fused qkv projection and output
+projection (``ops.gemm_bf16``), rotary embedding (``df_rope_bf16``), causal attention
+(``ops.attention_prefill``, reading q, k, v as column ranges of the fused qkv rows and writing
+the rows the output projection reads -- no transposes; the reference leaves this subgraph to the
+host model's kernels, ``examples/ae/scheduler/vllm/nanoflow.py:91-94``), the gated MLP
+(``ops.gated_mlp``), and between the blocks the reduce-scatter / residual add / RMSNorm /
+all-gather kernel on the communication stream (single rank: the stand-alone add + RMSNorm
+kernel). Head dimension 128 only.
 
 Schedule: the requests are cut into micro-batches; for every half-block (attention part,
 MLP part) the micro-batches run in order on the compute stream, and the reduction of
@@ -22,7 +23,6 @@ from __future__ import annotations
 import dataclasses
 
 import torch
-import torch.nn.functional as F
 
 from . import _native, ops
 from .comm import MulticastComm, PeerComm, add_rmsnorm
@@ -48,6 +48,8 @@ class TensorParallelDecoder:
         s = shape
         if s.heads % world or s.kv_heads % world or s.intermediate % world:
             raise ValueError("heads, kv heads and the intermediate size must divide evenly across ranks")
+        if s.head_dim != 128:
+            raise ValueError("the attention kernel is built for a head dimension of 128")
         self.s, self.rank, self.world = s, rank, world
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.micro_batches = micro_batches
@@ -114,14 +116,12 @@ class TensorParallelDecoder:
                                    s.rope_theta, torch.cuda.current_stream(self.device).cuda_stream)
         if rc != 0:
             raise RuntimeError(_native.last_error())
-        q = qkv[:, :self.q_cols].view(batch, seq, self.qh, s.head_dim).transpose(1, 2)
-        k = qkv[:, self.q_cols:self.q_cols + self.kv_cols].view(batch, seq, self.kvh, s.head_dim).transpose(1, 2)
-        v = qkv[:, self.q_cols + self.kv_cols:].view(batch, seq, self.kvh, s.head_dim).transpose(1, 2)
-        o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.qh != self.kvh)
         attn = self.attn_out[mb][:rows]
-        attn.view(batch, seq, self.qh, s.head_dim).copy_(o.transpose(1, 2))
+        ops.attention_prefill(qkv[:, :self.q_cols], qkv[:, self.q_cols:self.q_cols + self.kv_cols],
+                              qkv[:, self.q_cols + self.kv_cols:], attn, batch=batch, seq_len=seq,
+                              max_ctas=self.gemm_max_ctas)
         ops.gemm_bf16(attn, layer["wo"], out=self._partial(mb, rows), max_ctas=self.gemm_max_ctas)
-        self.launch_count += 3
+        self.launch_count += 4
 
     def _mlp_half(self, layer: dict, x: torch.Tensor, mb: int, rows: int) -> None:
         ops.gated_mlp(x, layer["wg"], layer["wu"], layer["wd"], out=self._partial(mb, rows), workspace=self.workspace[mb],

@@ -12,9 +12,19 @@ Pinning status
     (``tests/golden/make_golden.py`` wrote ``tests/golden/*.json|*.pt`` from it).
   * gated MLP: PINNED to the reference's own PyTorch execution of the split MLP
     graph on CPU (same fixtures); the GPU kernels are compared within 2e-2.
-  * all-reduce + residual + RMSNorm and the top-2 MoE routing: the arithmetic lives
-    in third-party code that is not part of the reference tree (flashinfer,
-    unpinned; vLLM @2dda3e35 ``RMSNorm``; vLLM fused-MoE routing), and the reference
-    has no vectors for it: PARITY UNPINNED. The restatement follows the call sites
-    and the in-tree kernel ``tokenweave.cu:38-113``.
+  * residual add + RMSNorm after the all-reduce: PINNED. The reference engine executed
+    ``residual + y`` followed by transformers' ``LlamaRMSNorm`` (bf16, eps 1e-5) in two
+    ragged nano-batches (``tests/golden/norm_split.*``); the oracle reproduces output and
+    new residual bit for bit. The cross-rank sum itself (NCCL / flashinfer / NVLS in the
+    reference's hosts) cannot run in the build container: the fixture feeds the module the
+    fp32 rank-order sum of four stored partials, which is the oracle's definition of it.
+  * top-2 MoE: PINNED to the reference engine's execution of a Mixtral-style block whose
+    router arithmetic is transformers' ``MixtralTopKRouter`` (``tests/golden/moe_split.*``):
+    expert ids and routing weights bit for bit, the layer output bit for bit with the
+    operator-chain expert form and within 2e-2 in the fused-epilogue form. The fixture has
+    no tied logits (``torch.topk`` does not specify their order); ties resolve to the lower
+    expert index here and in the CUDA kernel.
+  * causal attention: the reference treats it as an opaque subgraph run by the host's
+    kernels; the oracle states ``scaled_dot_product_attention(is_causal=True)`` in fp32 and
+    is checked against PyTorch's own implementation in ``tests/test_oracle_golden.py``.
 """

@@ -65,7 +65,9 @@ def allreduce_add_rmsnorm(partials: list[torch.Tensor], residual: torch.Tensor |
 def top2_route(router_logits: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """Mixtral-style routing: softmax over experts in fp32, top-2, renormalise.
     Returns ``(weights [T,2] fp32, expert ids [T,2] int64)``; ties resolve to the
-    lower expert index."""
+    lower expert index (``torch.topk`` leaves the order of equal values unspecified; the
+    serving stacks' routing kernels prefer the lower index, and so do this oracle and the
+    CUDA kernel)."""
     probs = torch.softmax(router_logits.float(), dim=-1)
     order = torch.sort(probs, dim=-1, descending=True, stable=True)   # stable: equal values keep index order
     w, ids = order.values[..., :2], order.indices[..., :2]
@@ -74,18 +76,21 @@ def top2_route(router_logits: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]
 
 
 def moe_layer(x: torch.Tensor, router_logits: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
-              w_down: torch.Tensor) -> torch.Tensor:
+              w_down: torch.Tensor, mlp=None) -> torch.Tensor:
     """Top-2 mixture of gated-MLP experts: dispatch = index gather of the rows routed
     to an expert, combine = weighted scatter-add in fp32, rounded once at the end.
     ``w_gate, w_up: [E, I, H]``, ``w_down: [E, H, I]``. The three-way operator split
-    dispatch / expert / combine is ``examples/ae/patch/vllm.patch:308-379, 423-527``."""
+    dispatch / expert / combine is ``examples/ae/patch/vllm.patch:308-379, 423-527``.
+    ``mlp`` selects the expert's operator chain (default: ``gated_mlp``, the fused-epilogue
+    rounding; ``gated_mlp_hf`` reproduces the reference-executed fixture bit for bit)."""
+    mlp = mlp or gated_mlp
     weights, ids = top2_route(router_logits)
     out = torch.zeros(x.shape, dtype=torch.float32)
     for e in range(w_gate.shape[0]):
         rows, slot = torch.nonzero(ids == e, as_tuple=True)
         if rows.numel() == 0:
             continue
-        y = gated_mlp(x[rows], w_gate[e], w_up[e], w_down[e])
+        y = mlp(x[rows], w_gate[e], w_up[e], w_down[e])
         out.index_add_(0, rows, y.float() * weights[rows, slot].unsqueeze(-1))
     return out.to(x.dtype)
 

@@ -16,6 +16,10 @@ the reference is modified. Outputs:
     dbo_trace.json       execution order and streams of the reference's DBO (MoE) policy
     mlp_split.npz/.json  bf16 gated-MLP graph executed by the reference in two
                          ragged nano-batches (inputs, weights, output)
+    norm_split.npz/.json residual add + RMSNorm (Hugging Face's LlamaRMSNorm, bf16, eps 1e-5)
+                         executed by the reference in two ragged nano-batches
+    moe_split.npz/.json  Mixtral-style top-2 mixture of gated-MLP experts (router arithmetic of
+                         Hugging Face's MixtralTopKRouter) executed the same way
 """
 from __future__ import annotations
 
@@ -32,7 +36,7 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REPO = os.path.dirname(os.path.dirname(HERE))
-REFERENCE = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REFERENCE = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("DYNAFLOW_REFERENCE", "/root/reference")
 
 
 class _InertEvent:
@@ -169,6 +173,107 @@ def run_reference(model, inputs, split, pattern, tag, ref):
     tags = {name: sorted(getattr(manager.graph_module.__dict__[name], "tag", set()))
             for name in manager.engine.module_name_to_node}
     return out, trace, tags
+
+
+
+def bits(t: torch.Tensor):
+    """bf16 tensors are stored as their int16 bit patterns (numpy has no bf16)."""
+    return t.detach().contiguous().view(torch.int16).numpy().copy()
+
+
+class AddRMSNorm(torch.nn.Module):
+    """The residual add and the normalisation that follow an all-reduce in a Hugging Face Llama
+    decoder layer (``hidden = residual + hidden; hidden = post_attention_layernorm(hidden)``):
+    the pair of operators the reference's policies match together with the collective
+    (``examples/ae/scheduler/vllm/nanoflow.py:59-69, 171-211``). The normalisation is
+    transformers' own ``LlamaRMSNorm``."""
+
+    def __init__(self, hidden: int, eps: float) -> None:
+        super().__init__()
+        from transformers.models.llama.modeling_llama import LlamaRMSNorm
+
+        self.norm = LlamaRMSNorm(hidden, eps)
+
+    def forward(self, y: torch.Tensor, residual: torch.Tensor):
+        r = residual + y
+        return self.norm(r), r
+
+
+class Top2MoE(torch.nn.Module):
+    """Mixtral-style block on given router logits: softmax in fp32, top-2, renormalise
+    (the arithmetic of transformers' ``MixtralTopKRouter.forward``), every expert a gated MLP
+    (``act(gate) * up`` then ``down``, as ``MixtralExperts`` computes one expert), combined as a
+    weighted sum in fp32. Written densely (every expert sees every token, unselected ones get
+    weight zero) so that it traces into one FX graph with a dynamic token dimension."""
+
+    def __init__(self, hidden: int, inter: int, experts: int) -> None:
+        super().__init__()
+        self.gate_up = torch.nn.Parameter(torch.empty(experts, 2 * inter, hidden))
+        self.down = torch.nn.Parameter(torch.empty(experts, hidden, inter))
+
+    def forward(self, x: torch.Tensor, router_logits: torch.Tensor):
+        F = torch.nn.functional
+        probs = F.softmax(router_logits.float(), dim=-1)
+        top_w, top_i = torch.topk(probs, 2, dim=-1)
+        top_w = top_w / top_w.sum(dim=-1, keepdim=True)
+        dense = torch.zeros_like(probs).scatter(1, top_i, top_w)
+        out = torch.zeros_like(x, dtype=torch.float32)
+        for e in range(self.gate_up.shape[0]):
+            gate, up = F.linear(x, self.gate_up[e]).chunk(2, dim=-1)
+            y = F.linear(F.silu(gate) * up, self.down[e])
+            out = out + y.float() * dense[:, e:e + 1]
+        return out.to(x.dtype), top_i, top_w
+
+
+def golden_norm_and_moe(ref) -> None:
+    import numpy as np
+
+    split = dict(num_nano_batches=2, batch_sizes=[40, 56], batch_indices=[0, 40, 96], num_tokens=[40, 56],
+                 num_tokens_padded=[40, 56], split_indices=[0, 40, 96], is_dryrun=False, use_cudagraph=False)
+    gen = torch.Generator().manual_seed(11)
+    M, H = 96, 256
+    mod = AddRMSNorm(H, 1e-5)
+    with torch.no_grad():
+        mod.norm.weight.copy_(1 + 0.1 * torch.randn(H, generator=gen))
+    mod = mod.to(torch.bfloat16).eval()
+    # four ranks' partial sums; the collective itself (NCCL in the reference's hosts) cannot run
+    # here, so the module is given their fp32 rank-order sum rounded to bf16
+    partials = [torch.randn(M, H, generator=gen).to(torch.bfloat16) for _ in range(4)]
+    acc = torch.zeros(M, H)
+    for p in partials:
+        acc += p.float()
+    y = acc.to(torch.bfloat16)
+    residual = torch.randn(M, H, generator=gen).to(torch.bfloat16)
+    (out, new_res), trace, tags = run_reference(mod, (y, residual), split, r"rsqrt", "norm", ref)
+    np.savez_compressed(os.path.join(HERE, "norm_split.npz"), y=bits(y), residual=bits(residual),
+                        weight=bits(mod.norm.weight), out=bits(out.clone()), new_residual=bits(new_res.clone()),
+                        **{f"partial{r}": bits(p) for r, p in enumerate(partials)})
+    with open(os.path.join(HERE, "norm_split.json"), "w") as f:
+        json.dump({"split": split, "trace": trace, "tags": tags, "eps": 1e-5, "dtype": "bfloat16 as int16 bits"}, f,
+                  indent=1)
+
+    gen = torch.Generator().manual_seed(12)
+    H, I, E = 64, 96, 8
+    moe = Top2MoE(H, I, E)
+    with torch.no_grad():
+        for p in moe.parameters():
+            p.copy_(torch.randn(p.shape, generator=gen) * 0.08)
+    moe = moe.to(torch.bfloat16).eval()
+    x = torch.randn(M, H, generator=gen).to(torch.bfloat16)
+    # No two experts of a token get equal logits: how torch.topk orders equal values is not
+    # specified (on this build it does not prefer the lower index), so ties pin nothing.
+    logits = (torch.randn(M, E, generator=gen) + 0.05 * torch.stack([torch.randperm(E, generator=gen).float()
+                                                                   for _ in range(M)])).to(torch.bfloat16)
+    for t in range(M):
+        while logits[t].unique().numel() < E:
+            logits[t] = (logits[t].float() + 0.03 * torch.randperm(E, generator=gen).float()).to(torch.bfloat16)
+    (out, ids, w), trace, tags = run_reference(moe, (x, logits), split, r"topk", "route", ref)
+    np.savez_compressed(os.path.join(HERE, "moe_split.npz"), x=bits(x), logits=bits(logits), gate_up=bits(moe.gate_up),
+                        down=bits(moe.down), out=bits(out.clone()), ids=ids.clone().numpy().astype(np.int64),
+                        weights=w.clone().numpy().astype(np.float32))
+    with open(os.path.join(HERE, "moe_split.json"), "w") as f:
+        json.dump({"split": split, "trace": trace, "tags": tags, "dtype": "bfloat16 as int16 bits; ids int64; weights fp32"},
+                  f, indent=1)
 
 
 def golden_dbo_trace(ref_iface, ref_cfg) -> dict:
@@ -323,14 +428,11 @@ def main() -> None:
     out, trace, tags = run_reference(mlp, (x,), split, r"silu", "act", ref)
     import numpy as np
 
-    def bits(t: torch.Tensor):
-        return t.detach().contiguous().view(torch.int16).numpy().copy()
-
-    # bf16 tensors are stored as their int16 bit patterns (numpy has no bf16)
     np.savez_compressed(os.path.join(HERE, "mlp_split.npz"), x=bits(x), w_gate=bits(mlp.gate_proj.weight),
                         w_up=bits(mlp.up_proj.weight), w_down=bits(mlp.down_proj.weight), out=bits(out.clone()))
     with open(os.path.join(HERE, "mlp_split.json"), "w") as f:
         json.dump({"split": split, "trace": trace, "tags": tags, "dtype": "bfloat16 as int16 bits"}, f, indent=1)
+    golden_norm_and_moe(ref)
     with open(os.path.join(HERE, "dbo_trace.json"), "w") as f:
         json.dump(golden_dbo_trace(ref_iface, ref_cfg), f, indent=1)
     print("golden fixtures written to", HERE)

@@ -142,7 +142,7 @@ def main() -> None:
     from dynaflow_b200.decoder import DecoderShape, TensorParallelDecoder, reference_weights
     from test_gpu_decoder import load_oracle_model, oracle_hidden
 
-    dshape = DecoderShape(hidden=256, intermediate=512, heads=8, kv_heads=8, head_dim=32, layers=2, vocab=256)
+    dshape = DecoderShape(hidden=256, intermediate=512, heads=8, kv_heads=8, head_dim=128, layers=2, vocab=256)
     dweights = reference_weights(dshape, seed=8)
     dids = torch.randint(0, dshape.vocab, (4, 64), generator=torch.Generator().manual_seed(9))
     dec = TensorParallelDecoder(dshape, rank=rank, world=world, max_rows=2 * 64, micro_batches=2, weights=dweights,

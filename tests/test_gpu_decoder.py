@@ -47,7 +47,7 @@ def test_decoder_stack_matches_pytorch_decoder(native_lib):
     from dynaflow_b200 import ops
     from dynaflow_b200.decoder import DecoderShape, TensorParallelDecoder, reference_weights
 
-    shape = DecoderShape(hidden=256, intermediate=512, heads=4, kv_heads=2, head_dim=64, layers=3, vocab=512)
+    shape = DecoderShape(hidden=256, intermediate=512, heads=4, kv_heads=2, head_dim=128, layers=3, vocab=512)
     weights = reference_weights(shape, seed=4)
     ids = torch.randint(0, shape.vocab, (6, 32), generator=torch.Generator().manual_seed(5))
     model = load_oracle_model(shape, weights).cuda()

@@ -244,3 +244,33 @@ def test_decode_rows_operand_swapped_form(ops, M, H, I):
         ops.set_launch_option("operand_swap", True)
     ops.check_status()
     assert rel_err(out, regular) <= 1e-2
+
+
+@pytest.mark.parametrize("M", [2048, 8192, 16384])
+def test_benchmark_shapes_against_oracle_on_sampled_rows(ops, M):
+    """The shapes every benchmark number is quoted on (hidden 4096, intermediate 14336; M rows in
+    two micro-batches of M/2, each ONE persistent launch): 24 sampled rows of every micro-batch,
+    among them the first and last row of the first and last 128-row panel, against the CPU oracle."""
+    from oracle import ops_oracle
+
+    H, I = 4096, 14336
+    g = torch.Generator(device="cuda").manual_seed(M)
+    x = torch.randn(M, H, device="cuda", generator=g).bfloat16()
+    wg = (torch.randn(I, H, device="cuda", generator=g) * 0.02).bfloat16()
+    wu = (torch.randn(I, H, device="cuda", generator=g) * 0.02).bfloat16()
+    wd = (torch.randn(H, I, device="cuda", generator=g) * 0.02).bfloat16()
+    half = M // 2
+    out = torch.empty(M, H, dtype=torch.bfloat16, device="cuda")
+    ws = torch.empty(ops.mlp_workspace_bytes(half, H, I), dtype=torch.uint8, device="cuda")
+    for mb in range(2):
+        ops.gated_mlp(x[mb * half:(mb + 1) * half], wg, wu, wd, out=out[mb * half:(mb + 1) * half], workspace=ws)
+    torch.cuda.synchronize()
+    ops.check_status()
+    pick = torch.randint(0, half, (16,), generator=torch.Generator().manual_seed(M + 1))
+    edge = torch.tensor([0, 127, 128, half // 2, half - 128, half - 1, 1, half - 2])
+    rows = torch.cat([torch.cat([pick, edge]) + mb * half for mb in range(2)])
+    want = ops_oracle.gated_mlp(x[rows].cpu(), wg.cpu(), wu.cpu(), wd.cpu())
+    assert rel_err(out[rows], want) <= TOL
+    # elementwise as well: no row may be off by more than the tolerance times its own magnitude scale
+    per_row = (out[rows].float().cpu() - want.float()).abs().amax(1) / want.float().abs().amax(1)
+    assert per_row.max().item() <= 2 * TOL

@@ -117,6 +117,37 @@ def test_single_rank_moe_layer_matches_oracle(lib, T, H, I, E):
     assert _rel(got, want) <= TOL
 
 
+def test_moe_layer_against_reference_executed_fixture(lib):
+    """The Mixtral-style top-2 block the reference engine executed in two ragged nano-batches
+    (tests/golden/moe_split.npz): expert ids bit-exact, routing weights to fp32 rounding, layer
+    output within the bf16 tolerance, nano-batch by nano-batch."""
+    import json
+    import os
+
+    import numpy as np
+
+    from conftest import GOLDEN
+    from dynaflow_b200 import ops
+    from dynaflow_b200.moe import ExpertParallelMoE
+
+    z = np.load(os.path.join(GOLDEN, "moe_split.npz"))
+    cuts = json.load(open(os.path.join(GOLDEN, "moe_split.json")))["split"]["split_indices"]
+    x, logits, gate_up, down, ref_out = (torch.from_numpy(z[k]).view(torch.bfloat16)
+                                         for k in ("x", "logits", "gate_up", "down", "out"))
+    E, inter, H = gate_up.shape[0], gate_up.shape[1] // 2, gate_up.shape[2]
+    weights = (gate_up[:, :inter].contiguous(), gate_up[:, inter:].contiguous(), down)
+    for i in range(2):
+        sl = slice(cuts[i], cuts[i + 1])
+        T = cuts[i + 1] - cuts[i]
+        layer = ExpertParallelMoE(H, inter, E, T, weights=weights, slots=1)
+        got = layer.forward(x[sl].cuda(), logits[sl].cuda())
+        torch.cuda.synchronize()
+        ops.check_status()
+        assert torch.equal(layer.ids[0].cpu().long(), torch.from_numpy(z["ids"])[sl])
+        assert torch.allclose(layer.route_w[0].cpu(), torch.from_numpy(z["weights"])[sl], rtol=1e-5, atol=1e-6)
+        assert _rel(got, ref_out[sl]) <= TOL
+
+
 @pytest.mark.parametrize("world,T,H", [(2, 64, 256), (8, 800, 1024), (4, 36, 64)])
 def test_emulated_all_gather_and_reduce_scatter(lib, world, T, H):
     """The two halves of the all-reduce as collectives of their own (expert parallelism)."""

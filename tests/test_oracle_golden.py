@@ -72,6 +72,41 @@ def test_gated_mlp_oracle_matches_reference_execution():
     assert rel <= 2e-2
 
 
+def test_allreduce_add_rmsnorm_oracle_matches_reference_execution():
+    """The residual add + RMSNorm (transformers' LlamaRMSNorm, bf16, eps 1e-5) that the reference
+    engine executed in two ragged nano-batches: the oracle reproduces both outputs bit for bit,
+    from the four ranks' partial sums (their fp32 rank-order sum is what the module was fed)."""
+    z = np.load(os.path.join(GOLDEN, "norm_split.npz"))
+    parts = [_bf16(z[f"partial{r}"]) for r in range(4)]
+    residual, weight = _bf16(z["residual"]), _bf16(z["weight"])
+    eps = _load("norm_split.json")["eps"]
+    out, new_res = ops_oracle.allreduce_add_rmsnorm(parts, residual, weight, eps=eps)
+    assert torch.equal(out, _bf16(z["out"])) and torch.equal(new_res, _bf16(z["new_residual"]))
+    out1, res1 = ops_oracle.allreduce_add_rmsnorm([_bf16(z["y"])], residual, weight, eps=eps)
+    assert torch.equal(out1, out) and torch.equal(res1, new_res)
+    cuts = _load("norm_split.json")["split"]["split_indices"]
+    for i in range(2):                                   # per nano-batch, as the engine ran it
+        sl = slice(cuts[i], cuts[i + 1])
+        o, r = ops_oracle.allreduce_add_rmsnorm([p[sl] for p in parts], residual[sl], weight, eps=eps)
+        assert torch.equal(o, _bf16(z["out"])[sl]) and torch.equal(r, _bf16(z["new_residual"])[sl])
+
+
+def test_top2_moe_oracle_matches_reference_execution():
+    """The Mixtral-style top-2 block the reference engine executed in two ragged nano-batches:
+    expert ids and routing weights bit for bit; the layer output bit for bit with the experts in
+    the operator-chain form the fixture ran, and within the bf16 tolerance in the fused-epilogue
+    form the CUDA kernels implement."""
+    z = np.load(os.path.join(GOLDEN, "moe_split.npz"))
+    x, logits, gate_up, down, ref_out = (_bf16(z[k]) for k in ("x", "logits", "gate_up", "down", "out"))
+    w, ids = ops_oracle.top2_route(logits)
+    assert torch.equal(ids, torch.from_numpy(z["ids"])) and torch.equal(w, torch.from_numpy(z["weights"]))
+    inter = gate_up.shape[1] // 2
+    wg, wu = gate_up[:, :inter], gate_up[:, inter:]
+    assert torch.equal(ops_oracle.moe_layer(x, logits, wg, wu, down, mlp=ops_oracle.gated_mlp_hf), ref_out)
+    fused = ops_oracle.moe_layer(x, logits, wg, wu, down)
+    assert ((fused.float() - ref_out.float()).abs().max() / ref_out.float().abs().max()).item() <= 2e-2
+
+
 def test_allreduce_add_rmsnorm_oracle_properties():
     g = torch.Generator().manual_seed(3)
     parts = [torch.randn(5, 64, generator=g).bfloat16() for _ in range(4)]
@@ -111,3 +146,20 @@ def test_dbo_trace_matches_reference_policy():
         program = [(n, t) for n, t in case["program"]]
         got = split_oracle.dbo_trace([program] * case["batches"])
         assert [list(x) for x in got] == case["trace"], (case["layers"], case["batches"])
+
+
+def test_causal_attention_oracle_matches_pytorch_sdpa():
+    """The attention restatement against torch's own scaled_dot_product_attention (the operator
+    the CPU parity configuration's decoder calls), ragged sequences, grouped heads, fp32."""
+    g = torch.Generator().manual_seed(21)
+    lens, hq, hkv, d = [5, 33, 1], 4, 2, 16
+    T = sum(lens)
+    q, k, v = (torch.randn(T, h, d, generator=g) for h in (hq, hkv, hkv))
+    got = ops_oracle.causal_attention(q, k, v, lens)
+    start = 0
+    for n in lens:
+        qs, ks, vs = (t[start:start + n].transpose(0, 1).unsqueeze(0) for t in (q, k, v))
+        want = torch.nn.functional.scaled_dot_product_attention(
+            qs, ks.repeat_interleave(hq // hkv, dim=1), vs.repeat_interleave(hq // hkv, dim=1), is_causal=True)
+        assert torch.allclose(got[start:start + n], want[0].transpose(0, 1), atol=1e-5, rtol=1e-5)
+        start += n

@@ -54,6 +54,11 @@ def test_static_scratch_entry_point_matches_workspace_entry_point(native_lib):
         ops.check_status()
         assert torch.isfinite(got.float()).all(), f"call {call}: output not fully written"
         assert _rel(got, want) <= TOL, f"call {call}"
+        # and against the CPU oracle, not only against the library's other entry point
+        from oracle import ops_oracle
+
+        oracle = ops_oracle.gated_mlp(x.cpu(), w_gate.cpu(), w_up.cpu(), w_down.cpu())
+        assert _rel(got.cpu(), oracle) <= TOL, f"call {call} vs oracle"
     # the tensor-level wrapper goes through the same entry point
     x = _rand((64, H), 1.0, 12)
     out = torch.empty(64, H, dtype=torch.bfloat16, device="cuda")
