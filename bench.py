@@ -7,13 +7,19 @@ Workload (the single-GPU configuration of the fused-MLP metric): X [16384, 4096]
 bf16 N(0,1), W_gate / W_up [14336, 4096], W_down [4096, 14336] bf16 N(0, 0.02),
 out = (silu(X W_gate^T) * (X W_up^T)) W_down^T, executed as two micro-batches of
 8192 rows. One "step" is one pass over the 16384 rows. With N > 1 the layer is
-tensor-parallel (intermediate dimension sharded N ways, partial outputs reduced
-across ranks, the reduction of micro-batch i overlapped with the GEMMs of i+1).
+tensor-parallel (intermediate dimension sharded N ways) and a step is one block of a
+DEPENDENT chain, the way a decoder stacks them: x <- rmsnorm(allreduce(mlp(x)) + residual),
+the reduction of micro-batch i under the GEMMs of micro-batch i+1.
 
 Prints ONE JSON line on rank 0. ``value`` is tokens/s with inputs resident in HBM,
-``e2e`` the same metric with host buffers and the copies inside the timed region.
-``--impl reference`` times the CPU restatement of the reference's operator chain
-on the host cores instead (a bounded sample per step).
+``e2e`` the same metric with host buffers and the copies inside the timed region,
+``parity`` the result check made before the timed region (sampled rows against the
+CPU oracle; at N > 1 also that every rank holds identical bits), ``decoder`` the
+Llama-3-8B-shaped prefill (32 layers, ids 8 x 2048, two micro-batches) on the same
+kernels with the fraction of communication hidden, ``torch_chain`` the operator chain
+the reference's host model runs on the GPU (cuBLAS linear, silu * mul, cuBLAS linear)
+timed beside the fused kernel. ``--impl reference`` times the reference package itself
+on the host cores (a bounded sample per step).
 """
 from __future__ import annotations
 
@@ -25,6 +31,7 @@ import subprocess
 import sys
 import threading
 import time
+import traceback
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
@@ -33,10 +40,11 @@ if ROOT not in sys.path:
 H, I = 4096, 14336
 ROWS = 16384
 MICRO_BATCHES = 2
-# dram__bytes_read.sum + dram__bytes_write.sum of one single-launch MLP (8192 rows, one GPU) from the 1-pass ncu
-# capture summarised in profiles/gated_mlp_launch_list_rows16384.md; it only describes that shape
+# dram__bytes_read.sum + dram__bytes_write.sum of one single-launch MLP of 8192 rows on one GPU (one-pass ncu
+# capture of this script); it only describes that shape
 MLP_DRAM_BYTES_PER_LAUNCH = 1_633_166_336 + 296_816_640
 METRIC = "prefill tokens/sec through the fused gated-MLP layer (2 micro-batches)"
+TOL = 2e-2
 
 
 def measured_peaks() -> tuple[dict, str]:
@@ -98,27 +106,17 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------ CPU arm
-def cpu_port_sample(target_seconds: float = 12.0, rows: int = 2048) -> tuple[float, float, int]:
-    """Times the oracle's gated MLP (the reference's operator chain restated on PyTorch CPU ops,
-    bf16, all host threads): passes over the same ``rows`` rows of the workload, after one untimed
-    pass, until ``target_seconds`` of CPU work are done. Returns (tokens/s, seconds, passes)."""
+def host_threads() -> int:
+    """All host cores, whatever OMP_NUM_THREADS the launcher exported (torch.distributed.run sets 1)."""
     import torch
 
-    from oracle import ops_oracle
-
-    wg, wu, wd = cpu_weights()
-    x = torch.randn(rows, H, generator=torch.Generator().manual_seed(1)).bfloat16()
-    passes = 0
-    with torch.inference_mode():
-        ops_oracle.gated_mlp(x, wg, wu, wd)
-        t0 = time.perf_counter()
-        while True:
-            ops_oracle.gated_mlp(x, wg, wu, wd)
-            passes += 1
-            elapsed = time.perf_counter() - t0
-            if elapsed >= target_seconds or passes >= 10000:
-                break
-    return rows * passes / elapsed, elapsed, passes
+    n = os.cpu_count() or 1
+    try:
+        n = len(os.sched_getaffinity(0)) or n
+    except (AttributeError, OSError):
+        pass
+    torch.set_num_threads(n)
+    return torch.get_num_threads()
 
 
 def cpu_weights():
@@ -131,8 +129,153 @@ def cpu_weights():
     return wg, wu, wd
 
 
+def cpu_sample(target_seconds: float = 12.0, rows: int = 2048) -> dict:
+    """The CPU baseline leg: the reference package itself (when installed under baseline/_ref; else
+    the oracle's restatement of its operator chain) on all host threads, bf16: passes over the same
+    ``rows`` rows of the workload, after one untimed pass, until ``target_seconds`` of CPU work
+    are done."""
+    import torch
+
+    from oracle import ops_oracle
+
+    cores = host_threads()
+    step, how = reference_package_step()
+    kind = "reference"
+    if step is None:
+        wg, wu, wd = cpu_weights()
+        kind = "port"
+
+        def step(x):
+            with torch.inference_mode():
+                return ops_oracle.gated_mlp(x, wg, wu, wd)
+
+    x = torch.randn(rows, H, generator=torch.Generator().manual_seed(1)).bfloat16()
+    passes = 0
+    step(x)
+    t0 = time.perf_counter()
+    while True:
+        step(x)
+        passes += 1
+        elapsed = time.perf_counter() - t0
+        if elapsed >= target_seconds or passes >= 10000:
+            break
+    return {"value": rows * passes / elapsed, "unit": "tokens/s", "cores": cores, "kind": kind,
+            "sample": f"{rows} of {ROWS} rows in two nano-batches, {passes} passes in {elapsed:.1f} s (bf16, torch CPU); {how}"}
+
+
+def reference_package_step():
+    """The reference package (installed unmodified under baseline/_ref) running the gated-MLP graph on
+    the CPU in two nano-batches through its own manager, engine and executor; the policy is the
+    round-robin schedule its examples use, written here against its public interface (its example
+    policies are not part of the installed package). Returns ``(step(x) -> out, description)`` or
+    ``(None, why)``."""
+    import torch
+
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "dynaflow")):
+        return None, "baseline/_ref holds no installed reference package"
+    sys.path.insert(0, ref_dir)
+    try:
+        import dynaflow.config as rcfg
+        import dynaflow.interface as riface
+        import dynaflow.manager as rmanager
+        import dynaflow.matching as rmatching
+    except Exception as exc:  # noqa: BLE001
+        return None, f"the reference package does not import: {exc}"
+    if not torch.cuda.is_available():
+        # the reference's engine records CUDA events around every operator; without a driver they are inert
+        import contextlib
+
+        class _Inert:
+            def __init__(self, *a, **k):
+                pass
+
+            def record(self, *a, **k):
+                pass
+
+            def wait(self, *a, **k):
+                pass
+
+            def synchronize(self):
+                pass
+
+        torch.cuda.Event = _Inert  # type: ignore[misc]
+        torch.cuda.Stream = _Inert  # type: ignore[misc]
+        torch.cuda.stream = lambda s: contextlib.nullcontext()  # type: ignore[assignment]
+
+    class RoundRobin(riface.OpSchedulerBase):
+        def __init__(self):
+            super().__init__(policy_name="round-robin")
+
+        def get_split_rules(self):
+            return [rmatching.MatchingRule(condition=rmatching.Op(pattern=r"silu"))]
+
+        def get_tag_rules(self):
+            return {rmatching.MatchingRule(condition=rmatching.Op(pattern=r"silu")): {"act"}}
+
+        def get_split_config(self, input_info, use_cudagraph):
+            raise NotImplementedError("the bench overrides the split")
+
+        async def schedule(self, context):
+            live = list(range(context.split_config.num_nano_batches))
+            while live:
+                ops = []
+                for b in list(live):
+                    op = await context.pop(b)
+                    if op is None:
+                        live.remove(b)
+                    else:
+                        ops.append(op)
+                for op in ops:
+                    await context.execute((op,))
+
+    class GatedMLP(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            wg, wu, wd = cpu_weights()
+            self.gate_proj = torch.nn.Linear(H, I, bias=False, dtype=torch.bfloat16)
+            self.up_proj = torch.nn.Linear(H, I, bias=False, dtype=torch.bfloat16)
+            self.down_proj = torch.nn.Linear(I, H, bias=False, dtype=torch.bfloat16)
+            with torch.no_grad():
+                self.gate_proj.weight.copy_(wg)
+                self.up_proj.weight.copy_(wu)
+                self.down_proj.weight.copy_(wd)
+
+        def forward(self, x):
+            return self.down_proj(torch.nn.functional.silu(self.gate_proj(x)) * self.up_proj(x))
+
+    cfg = rcfg.DynaFlowConfig("bench:RoundRobin", 2, rcfg.InductorConfig(False), rcfg.CUDAGraphConfig(False, [64]), {})
+    manager = rmanager.DynaFlowManager()
+    policy = RoundRobin()
+
+    def backend(gm, example_inputs):
+        manager.initialize(graph_module=gm, config=cfg, scheduler=policy, example_inputs=list(example_inputs))
+        return manager.get_callable()
+
+    model = GatedMLP().eval()
+    torch._dynamo.reset()
+    compiled = torch.compile(model, backend=backend, fullgraph=True)
+
+    def step(x):
+        import contextlib
+        import io
+
+        rows = x.shape[0]
+        half = rows // 2
+        torch._dynamo.mark_dynamic(x, 0)
+        manager.override_split_config(riface.SplitConfig(
+            num_nano_batches=2, batch_sizes=[half, rows - half], batch_indices=[0, half, rows],
+            num_tokens=[half, rows - half], num_tokens_padded=[half, rows - half], split_indices=[0, half, rows],
+            is_dryrun=False, use_cudagraph=False))
+        with torch.inference_mode(), contextlib.redirect_stdout(io.StringIO()):
+            return compiled(x)
+
+    return step, "reference package (baseline/_ref, unmodified): DynaFlowManager + engine on the gated-MLP graph, 2 nano-batches"
+
+
 def run_reference_arm(args) -> None:
-    """CPU implementation of the path on the host cores, all threads, bounded sample per step."""
+    """The reference's CPU implementation of the path on the host cores, all threads, a bounded
+    sample of the workload per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -140,33 +283,48 @@ def run_reference_arm(args) -> None:
 
     from oracle import ops_oracle
 
-    cores = torch.get_num_threads()
-    wg, wu, wd = cpu_weights()
+    cores = host_threads()
+    step, how = reference_package_step()
+    kind = "reference"
+    if step is None:
+        # no installed reference package: the oracle's restatement of its operator chain
+        wg, wu, wd = cpu_weights()
+        kind, how = "port", f"oracle port ({how})"
+
+        def step(x):
+            with torch.inference_mode():
+                return ops_oracle.gated_mlp(x, wg, wu, wd)
+
     g = torch.Generator().manual_seed(1)
-    probe = torch.randn(16, H, generator=g).bfloat16()
-    with torch.inference_mode():
-        ops_oracle.gated_mlp(probe, wg, wu, wd)
-        t0 = time.perf_counter()
-        ops_oracle.gated_mlp(probe, wg, wu, wd)
-        per_row = (time.perf_counter() - t0) / 16
+    probe = torch.randn(64, H, generator=g).bfloat16()
+    step(probe)                                   # traces / initialises
+    t0 = time.perf_counter()
+    step(probe)
+    per_row = (time.perf_counter() - t0) / 64
     budget = min(2.0, 150.0 / max(1, args.steps + args.warmup))
-    rows = int(max(16, min(ROWS, budget / per_row)) // 16 * 16)
+    rows = int(max(64, min(ROWS, budget / per_row)) // 16 * 16)
     x = torch.randn(rows, H, generator=g).bfloat16()
-    with torch.inference_mode():
-        for _ in range(args.warmup):
-            ops_oracle.gated_mlp(x, wg, wu, wd)
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            ops_oracle.gated_mlp(x, wg, wu, wd)
-        dt = time.perf_counter() - t0
+    for _ in range(max(1, args.warmup)):
+        out = step(x)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        out = step(x)
+    dt = time.perf_counter() - t0
+    # the arm's own result check: sampled rows against the oracle
+    pick = torch.arange(0, rows, max(1, rows // 8))[:8]
+    wg, wu, wd = cpu_weights()
+    want = ops_oracle.gated_mlp_hf(x[pick], wg, wu, wd)
+    rel = ((out[pick].float() - want.float()).abs().max() / want.float().abs().max()).item()
     value = rows * args.steps / dt
-    sample = f"{rows} of {ROWS} rows per step, {args.steps} steps, bf16, torch CPU"
+    sample = f"{rows} of {ROWS} rows per step (two nano-batches of {rows // 2}), {args.steps} steps, bf16, torch CPU, {cores} threads"
+    config = dict(workload_config(args.gpus), sample=sample)
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "config": config, "how": how,
+        "parity": {"checked": True, "max_rel_err": rel, "against": "oracle (operator-chain form), 8 sampled rows"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -201,25 +359,223 @@ def comm_plan(args, world: int, sms: int | None = None, multicast: bool | None =
     return {"comm": kind, "comm_ctas": comm_ctas, "gemm_ctas": gemm_ctas, "exclusive_sms": exclusive}
 
 
-# ------------------------------------------------------------------ GPU arm
-def run_ours(args) -> None:
+# ---------------------------------------------------------- rank coordination
+class PeerFailed(RuntimeError):
+    """Another rank reported a failure at a synchronisation point."""
+
+
+class RankSync:
+    """Every host-side collective of the run after the communicators exist has ONE shape (an
+    all-reduce MAX over five doubles: four values and a failure flag), so that a rank that fails
+    can still pair with whatever synchronisation its peers reach next, tell them, and all ranks
+    unmap their communicators together (a rank that exits while its memory is bound to an NVLink
+    multicast object can fault its peers' GPUs)."""
+
+    def __init__(self, world: int, device) -> None:
+        self.world, self.device = world, device
+
+    def reduce_max(self, values: list[float], fail: bool = False, quiet: bool = False) -> list[float]:
+        if self.world == 1:
+            return list(values)
+        import torch
+        import torch.distributed as dist
+
+        padded = list(values) + [float("-inf")] * (4 - len(values)) + [1.0 if fail else 0.0]
+        t = torch.tensor(padded, dtype=torch.float64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        out = t.tolist()
+        if out[4] > 0 and not fail and not quiet:
+            raise PeerFailed("another rank failed")
+        return out[:len(values)]
+
+    def barrier(self) -> None:
+        import torch
+
+        torch.cuda.synchronize()
+        self.reduce_max([0.0])
+
+    def max_ms(self, ms: float) -> float:
+        return self.reduce_max([ms])[0]
+
+    def all_equal(self, digest: float) -> bool:
+        hi, neg_lo = self.reduce_max([digest, -digest])
+        return hi == -neg_lo
+
+
+def digest_of(t) -> float:
+    """Order-independent exact checksum of a bf16 tensor's bits (fits a double exactly)."""
     import torch
-    import torch.distributed as dist
+
+    return float(t.contiguous().view(torch.int16).to(torch.int64).sum().item())
+
+
+# ------------------------------------------------------------------ GPU arm
+def parity_check(layer, comm, sync, rank: int, world: int, dev, x_dev, out_dev, cuts) -> dict:
+    """One step before the timed region, checked: 24 sampled rows of every micro-batch against the
+    CPU oracle (at N > 1 the fp32 rank-order sum of the per-shard oracle results), every rank
+    holding identical bits, and at N > 1 the fused residual + RMSNorm form of the reduction against
+    the oracle. Rank 0 evaluates the oracle; the others take part in the comparisons of bits."""
+    import torch
+
+    from dynaflow_b200 import ops
+    from dynaflow_b200.layer import shard_bounds
+    from oracle import ops_oracle
+
+    rows_mb = ROWS // MICRO_BATCHES
+    gen = torch.Generator().manual_seed(123)
+    pick = torch.cat([torch.randint(0, rows_mb, (16,), generator=gen),
+                      torch.tensor([0, 127, 128, rows_mb // 2, rows_mb - 128, rows_mb - 2, rows_mb - 1, 1])])
+    rows = torch.cat([pick + cuts[mb] for mb in range(MICRO_BATCHES)])
+    results: list = []
+    layer.forward_device(x_dev, out_dev, cuts, results=results)
+    torch.cuda.synchronize()
+    ops.check_status()
+    got_full = torch.cat(results) if world > 1 else out_dev
+    identical = sync.all_equal(digest_of(got_full))
+    got = got_full[rows.to(dev)].cpu()
+    report = {"checked": True, "ranks_identical": bool(identical), "rows_sampled": int(rows.numel()),
+              "against": "CPU oracle (oracle/ops_oracle.gated_mlp), fp32 rank-order sum of the per-shard results"}
+    fused_got = fused_res = None
+    if world > 1:
+        # fused form of the reduction on the same partial sums: residual and weight from a seed
+        g2 = torch.Generator().manual_seed(321)
+        residual = torch.randn(ROWS, H, generator=g2).bfloat16()
+        weight = (1 + 0.1 * torch.randn(H, generator=g2)).bfloat16()
+        res_dev = residual.to(dev)
+        outs = layer.forward_chain(x_dev, cuts, 1, weight.to(dev), res_dev, sharded_residual=True)
+        torch.cuda.synchronize()
+        ops.check_status()
+        fused_full = torch.cat(list(outs))
+        report["fused_ranks_identical"] = bool(sync.all_equal(digest_of(fused_full)))
+        fused_got = fused_full[rows.to(dev)].cpu()
+        fused_res = (residual, weight)
+    worst = fused_worst = 0.0
+    if rank == 0:
+        host_threads()
+        wg, wu, wd = cpu_weights()
+        xs = x_dev[rows.to(dev)].cpu()
+        parts = []
+        for r in range(world):
+            lo, hi = shard_bounds(I, r, world)
+            parts.append(ops_oracle.gated_mlp(xs, wg[lo:hi], wu[lo:hi], wd[:, lo:hi]))
+        acc = torch.zeros(xs.shape[0], H)
+        for p in parts:
+            acc += p.float()
+        want = acc.bfloat16()
+        worst = ((got.float() - want.float()).abs().max() / want.float().abs().max()).item()
+        if fused_got is not None:
+            residual, weight = fused_res
+            want_out, _ = ops_oracle.allreduce_add_rmsnorm(parts, residual[rows], weight)
+            fused_worst = ((fused_got.float() - want_out.float()).abs().max() / want_out.float().abs().max()).item()
+    worst, fused_worst = sync.reduce_max([worst, fused_worst])
+    report["max_rel_err"] = worst
+    if world > 1:
+        report["fused_add_rmsnorm_max_rel_err"] = fused_worst
+    report["tolerance"] = TOL
+    ok = identical and worst <= TOL and fused_worst <= TOL and report.get("fused_ranks_identical", True)
+    report["ok"] = bool(ok)
+    if not ok:
+        raise AssertionError(f"parity check failed: {report}")
+    return report
+
+
+def torch_chain_ms(layer, x_dev, cuts, steps: int) -> dict:
+    """The reference's own GPU operator chain for this layer, as its host model runs it inside a
+    compute subgraph: cuBLAS linear, silu * mul, cuBLAS linear, bf16, the same tensors and
+    micro-batches, timed in the same process outside the timed region of ``value``."""
+    import torch
+    import torch.nn.functional as F
+
+    def step():
+        for mb in range(len(cuts) - 1):
+            x = x_dev[cuts[mb]:cuts[mb + 1]]
+            F.linear(F.silu(F.linear(x, layer.w_gate)) * F.linear(x, layer.w_up), layer.w_down)
+
+    with torch.inference_mode():
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            step()
+        b.record()
+        torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / steps
+    return {"ms_per_step": ms, "tokens_per_s": ROWS / (ms * 1e-3), "steps": steps,
+            "what": "F.linear(gate), F.linear(up), silu * mul, F.linear(down) per micro-batch (cuBLAS + eager elementwise)"}
+
+
+def decoder_block(args, sync, closers, rank: int, world: int, dev, plan: dict) -> dict:
+    """Llama-3-8B-shaped decoder prefill (32 layers, hidden 4096, intermediate 14336, 32 query / 8
+    key-value heads of 128, ids 8 x 2048, two micro-batches), tensor parallel over the ranks:
+    tokens/s, fraction of the tensor peak and of the roofline, and at N > 1 how much of the
+    communication the schedule hides."""
+    import torch
+
+    from dynaflow_b200 import ops
+    from dynaflow_b200.decoder import DecoderShape, TensorParallelDecoder
+
+    shape = DecoderShape(layers=args.layers)
+    batch, seq = 8, 2048
+    dec = TensorParallelDecoder(shape, rank=rank, world=world, max_rows=batch * seq // MICRO_BATCHES,
+                                micro_batches=MICRO_BATCHES, seed=0, device=dev, n_ctas=max(plan["comm_ctas"], 1),
+                                multicast=plan["comm"] == "multicast", gemm_max_ctas=plan["gemm_ctas"])
+    closers.append(dec.close)
+    ids = torch.randint(0, shape.vocab, (batch, seq), generator=torch.Generator().manual_seed(1)).to(dev)
+
+    def timed(**kw):
+        for _ in range(2):
+            dec.forward(ids, **kw)
+        sync.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 3
+        a.record()
+        for _ in range(reps):
+            hidden = dec.forward(ids, **kw)
+        b.record()
+        sync.barrier()
+        return sync.max_ms(a.elapsed_time(b) / reps), hidden
+
+    t_all, hidden = timed()
+    ops.check_status()
+    identical = sync.all_equal(digest_of(hidden))
+    peaks, kind = measured_peaks()
+    s = shape
+    linear = 2.0 * (s.hidden * (s.heads + 2 * s.kv_heads) * s.head_dim + s.heads * s.head_dim * s.hidden
+                    + 3 * s.hidden * s.intermediate)
+    attn = 4.0 * ((seq + 1) / 2) * s.heads * s.head_dim
+    flops = (linear + attn) * s.layers * batch * seq
+    peak = float(peaks["bf16_tflops"])
+    out = {"workload": f"Llama-3-8B-shaped decoder prefill, {s.layers} layers, ids {batch}x{seq}, "
+                       f"{MICRO_BATCHES} micro-batches, tp{world}; attention, GEMMs, RoPE, norms and reductions on "
+                       "this library's kernels",
+           "tokens_per_s": batch * seq / (t_all * 1e-3), "ms_per_forward": t_all, "flops_per_forward": flops,
+           "tflops_per_gpu": flops / world / (t_all * 1e-3) / 1e12,
+           "frac_of_tensor_peak": flops / world / (t_all * 1e-3) / 1e12 / peak,
+           "peak_source": f"{kind} cuBLAS bf16 burst", "ranks_identical": bool(identical)}
+    if world > 1:
+        t_compute, _ = timed(skip_comm=True)
+        t_comm, _ = timed(skip_compute=True)
+        payload = 2 * s.layers * batch * seq * s.hidden * 2
+        roofline_ms = max(flops / world / (peak * 1e12), (world - 1) / world * payload / 770e9) * 1e3
+        out.update({"ms_compute_only": t_compute, "ms_comm_only": t_comm,
+                    "hidden_frac": 1.0 - (t_all - t_compute) / t_comm,
+                    "wire_ms_at_770_gbs": (world - 1) / world * payload / 770e9 * 1e3,
+                    "roofline_ms": roofline_ms, "frac_of_roofline": roofline_ms / t_all})
+    else:
+        out["frac_of_roofline"] = out["frac_of_tensor_peak"]
+    ops.check_status()
+    return out
+
+
+def measure(args, sync, closers, rank: int, world: int, local_rank: int, dev) -> dict:
+    import torch
 
     from dynaflow_b200 import ops
     from dynaflow_b200.layer import TensorParallelGatedMLP
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-
-    comm = None
+    comm = comm_in = None
     plan = comm_plan(args, world)
     if world > 1:
         from dynaflow_b200.comm import MulticastComm, PeerComm, set_exclusive_sms
@@ -236,6 +592,9 @@ def run_ours(args) -> None:
                 plan = comm_plan(args, world)
         if comm is None:
             comm = PeerComm(rank, world, ROWS // MICRO_BATCHES, H, slots=MICRO_BATCHES, n_ctas=plan["comm_ctas"], device=dev)
+        closers.append(comm.close)
+        comm_in = PeerComm(rank, world, ROWS // MICRO_BATCHES, H, slots=MICRO_BATCHES, n_ctas=plan["comm_ctas"], device=dev)
+        closers.append(comm_in.close)
         set_exclusive_sms(plan["exclusive_sms"])
     layer = TensorParallelGatedMLP(H, I, rank=rank, world=world, max_rows=ROWS // MICRO_BATCHES,
                                    micro_batches=MICRO_BATCHES, seed=0, device=dev, comm=comm)
@@ -246,46 +605,54 @@ def run_ours(args) -> None:
     x_dev = x_host.to(dev)
     out_dev = torch.empty(ROWS, H, dtype=torch.bfloat16, device=dev)
     cuts = [ROWS * i // MICRO_BATCHES for i in range(MICRO_BATCHES + 1)]
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(ms: float) -> float:
-        if world == 1:
-            return ms
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    norm_w = torch.ones(H, dtype=torch.bfloat16, device=dev)
+    residual = torch.zeros(ROWS, H, dtype=torch.bfloat16, device=dev)
+    chain_kw = dict(fused_norm=args.fused_norm, sharded_residual=not args.replicated_residual)
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
 
-    # ---- device-resident: value, and per-kernel times for the roofline
-    # Consecutive steps pipeline like consecutive layers: the reduction of a step's last micro-batch
-    # runs under the next step's first GEMMs; the stream joins the reductions before the end mark.
-    for _ in range(args.warmup):
-        layer.forward_device(x_dev, out_dev, cuts, join=False)
-    layer.wait_reductions()
-    barrier()
-    marks = []
+    # ---- warm-up, then the result check, then the timed region
+    if world == 1:
+        for _ in range(args.warmup):
+            layer.forward_device(x_dev, out_dev, cuts)
+    else:
+        layer.forward_chain(x_dev, cuts, args.warmup, norm_w, residual, **chain_kw)
+    sync.barrier()
+    ops.check_status()
+    parity = parity_check(layer, comm, sync, rank, world, dev, x_dev, out_dev, cuts)
+    sync.barrier()
+
     t_wall0 = time.time()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(args.steps):
-        marks.append(layer.forward_device(x_dev, out_dev, cuts, record_kernel_events=True, join=False))
-    layer.wait_reductions()
-    end.record()
-    barrier()
+    if world == 1:
+        marks = []
+        start.record()
+        for _ in range(args.steps):
+            marks.append(layer.forward_device(x_dev, out_dev, cuts, record_kernel_events=True))
+        end.record()
+        sync.barrier()
+        mlp_ms = statistics.mean(m0.elapsed_time(m1) for step in marks for (m0, m1) in step)
+        launches = layer.launches_per_step * args.steps
+    else:
+        # K dependent blocks: x <- rmsnorm(allreduce(mlp(x)) + residual), the reduction of a micro-batch under
+        # the other micro-batch's GEMMs
+        residual.zero_()
+        timings: list = []
+        start.record()
+        layer.forward_chain(x_dev, cuts, args.steps, norm_w, residual, timings=timings, **chain_kw)
+        end.record()
+        sync.barrier()
+        mlp_ms = statistics.mean(t0.elapsed_time(t1) for kind, t0, t1 in timings if kind == "mlp")
+        launches = len(timings)
     t_wall1 = time.time()
-    ms_step = max_over_ranks(start.elapsed_time(end) / args.steps)
-    mlp_ms = statistics.mean(m0.elapsed_time(m1) for step in marks for (m0, m1) in step)
+    ms_step = sync.max_ms(start.elapsed_time(end) / args.steps)
     ops.check_status()
+
     # the same MLP as two launches, a few steps outside the timed region: how the time splits between the GEMMs
     for _ in range(2):
         layer.forward_device(x_dev, out_dev, cuts, record_kernel_events="split")
     split = [layer.forward_device(x_dev, out_dev, cuts, record_kernel_events="split") for _ in range(max(3, args.steps // 10))]
-    barrier()
+    sync.barrier()
     gateup_ms = statistics.median(m0.elapsed_time(m1) for step in split for (m0, m1, _m2) in step)
     down_ms = statistics.median(m1.elapsed_time(m2) for step in split for (_m0, m1, m2) in step)
     ops.check_status()
@@ -294,30 +661,27 @@ def run_ours(args) -> None:
     comm_stats = None
     if world > 1:
         chain_layers = 8
-        norm_w = torch.ones(H, dtype=torch.bfloat16, device=dev)
-        residual = torch.zeros(ROWS, H, dtype=torch.bfloat16, device=dev)
 
         def timed(**kw):
             for _ in range(2):
                 residual.zero_()
-                layer.forward_chain(x_dev, cuts, chain_layers, norm_w, residual, fused_norm=args.fused_norm, sharded_residual=not args.replicated_residual, **kw)
-            barrier()
+                layer.forward_chain(x_dev, cuts, chain_layers, norm_w, residual, **chain_kw, **kw)
+            sync.barrier()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             reps = max(4, args.steps // 16)
             a.record()
             for _ in range(reps):
-                layer.forward_chain(x_dev, cuts, chain_layers, norm_w, residual, fused_norm=args.fused_norm, sharded_residual=not args.replicated_residual, **kw)
+                layer.forward_chain(x_dev, cuts, chain_layers, norm_w, residual, **chain_kw, **kw)
             b.record()
-            barrier()
-            return max_over_ranks(a.elapsed_time(b) / reps / chain_layers)
+            sync.barrier()
+            return sync.max_ms(a.elapsed_time(b) / reps / chain_layers)
 
-        t_overlap = timed()
         t_compute = timed(skip_comm=True)
         t_comm = timed(skip_compute=True)
+        t_overlap = ms_step
         payload = ROWS * H * 2  # bytes reduced per block (all micro-batches)
-        wire = 2.0 * (world - 1) / world * payload
         peak_tf = float(measured_peaks()[0]["bf16_tflops"])
-        comm_stats = {"chain": f"{chain_layers} TP MLP blocks back to back; between them all-reduce + residual + RMSNorm: "
+        comm_stats = {"chain": "dependent TP MLP blocks; between them all-reduce + residual + RMSNorm: "
                                + ("reduce-scatter, add + norm on the owned rows (residual sharded by rows), all-gather, one launch"
                                   if not args.replicated_residual else
                                   ("replicated residual, one launch" if args.fused_norm
@@ -325,58 +689,79 @@ def run_ours(args) -> None:
                       "ms_per_block_overlapped": t_overlap, "ms_per_block_compute_only": t_compute,
                       "ms_per_block_comm_only": t_comm,
                       "hidden_frac": 1.0 - (t_overlap - t_compute) / t_comm,
-                      "bus_gbs_comm_only": wire / (t_comm * 1e-3) / 1e9,
+                      # an in-switch reduction moves the payload once per direction and GPU; the peer form (W-1)/W of it, twice
+                      "link_gbs_per_direction_comm_only": (payload if plan["comm"] == "multicast"
+                                                           else 2.0 * (world - 1) / world * payload) / (t_comm * 1e-3) / 1e9,
                       "nvlink_peak_gbs": 770.0, "nvlink_peak_source": "measured peer copy, per direction",
                       "roofline_ms_per_block": max(6.0 * ROWS * H * (I // world) / (peak_tf * 1e12),
-                                                   (world - 1) / world * payload / 770e9) * 1e3,
-                      "tokens_per_s_chain": ROWS / (t_overlap * 1e-3)}
+                                                   (world - 1) / world * payload / 770e9) * 1e3}
         comm_stats["frac_of_roofline_chain"] = comm_stats["roofline_ms_per_block"] / t_overlap
         ops.check_status()
 
     # ---- end to end: pinned host buffers, copies inside the timed region
+    if world == 1:
+        def e2e_step():
+            layer.forward_host(x_host, out_host, cuts)
+
+        h2d = d2h = ROWS * H * 2
+        e2e_note = "pinned host X -> H2D -> MLP -> D2H per micro-batch on its own stream (C ABI through TensorParallelGatedMLP)"
+    else:
+        # every rank owns 1/N of the rows of each micro-batch: it copies only those in and out
+        sizes = [comm.slice_bounds(cuts[i + 1] - cuts[i]) for i in range(MICRO_BATCHES)]
+        local = sum(hi - lo for lo, hi in sizes)
+        xl = torch.cat([x_host[cuts[i] + lo: cuts[i] + hi] for i, (lo, hi) in enumerate(sizes)]).pin_memory()
+        ol = torch.empty(local, H, dtype=torch.bfloat16).pin_memory()
+
+        def e2e_step():
+            layer.forward_host_sliced(xl, ol, cuts, comm_in)
+
+        h2d = d2h = ROWS * H * 2          # whole job: each of the N ranks moves 1/N of it
+        e2e_note = ("each rank copies its 1/N of the rows in, all-gather over NVLink, MLP, reduce-scatter, copies its "
+                    "1/N of the result out; bytes are the whole job's")
     for _ in range(args.warmup):
-        layer.forward_host(x_host, out_host, cuts)
-    barrier()
+        e2e_step()
+    sync.barrier()
     s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s2.record()
     for _ in range(args.steps):
-        layer.forward_host(x_host, out_host, cuts)
+        e2e_step()
     e2.record()
-    barrier()
-    e2e_ms = max_over_ranks(s2.elapsed_time(e2) / args.steps)
+    sync.barrier()
+    e2e_ms = sync.max_ms(s2.elapsed_time(e2) / args.steps)
     ops.check_status()
+    # the end-to-end result, checked too: sampled rows of what came back to the host against the device-resident run
+    if world == 1:
+        layer.forward_device(x_dev, out_dev, cuts)
+        torch.cuda.synchronize()
+        e2e_equal = bool(torch.equal(out_host[::509], out_dev[::509].cpu()))
+    else:
+        results = []
+        layer.forward_device(x_dev, out_dev, cuts, results=results)
+        torch.cuda.synchronize()
+        want_local = torch.cat([results[i][lo:hi] for i, (lo, hi) in enumerate(sizes)]).cpu()
+        rel = ((ol.float() - want_local.float()).abs().max() / want_local.float().abs().max()).item()
+        e2e_equal = bool(sync.reduce_max([rel])[0] <= TOL)   # peer-order sum vs the in-switch sum: within tolerance
     if sampler is not None:
         sampler.stop()
 
-    comm_summary = layer.comm_summary()
-    if world > 1:
-        # every rank leaves together: the regions are unmapped only once nobody can touch them any more
-        barrier()
-        comm.close()
-        dist.barrier()
-        dist.destroy_process_group()
-    if rank != 0:
-        return
+    chain = torch_chain_ms(layer, x_dev, cuts, args.steps) if world == 1 else None
+    decoder = None
+    if not args.no_decoder:
+        # free the MLP layer's activations first; the decoder brings its own buffers and communicator
+        decoder = decoder_block(args, sync, closers, rank, world, dev, plan)
 
     peaks, peak_kind = measured_peaks()
     rows_mb = ROWS // MICRO_BATCHES
     mlp_flops = 6.0 * rows_mb * H * (I // world)          # one launch: gate/up 4 M H I + down 2 M H I
     achieved = mlp_flops / (mlp_ms * 1e-3) / 1e12
-    # denominator: the measured cuBLAS burst figure; the kernel is timed inside the long, power-capped step, so the
-    # fraction of the measured SUSTAINED figure is printed beside it
     burst = float(peaks["bf16_tflops"])
-    peak = burst
     sustained = float(peaks.get("bf16_tflops_sustained", burst))
     step_flops = 6.0 * ROWS * H * (I // world)
     traffic = MLP_DRAM_BYTES_PER_LAUNCH if (ROWS == 16384 and world == 1) else None
 
     cpu = None
-    if world == 1 and not args.no_cpu_baseline:
-        rate, secs, passes = cpu_port_sample(12.0, 2048)
-        import torch as _t
-
-        cpu = {"value": rate, "unit": "tokens/s", "cores": _t.get_num_threads(), "kind": "port",
-               "sample": f"2048 of {ROWS} rows, {passes} passes of the oracle's gated MLP in {secs:.1f} s (bf16, torch CPU)"}
+    if world == 1 and not args.no_cpu_baseline and rank == 0:
+        cpu = cpu_sample(12.0, 2048)
 
     sweep = None
     if world == 1 and not args.no_sweep:
@@ -386,13 +771,15 @@ def run_ours(args) -> None:
         "metric": METRIC, "value": ROWS / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": dict(workload_config(world), **({"reduction": plan} if world > 1 else {})),
+        "config": dict(workload_config(world), **({"reduction": plan, "step": "one block of a dependent chain: MLP, "
+                                                   "all-reduce, residual add, RMSNorm"} if world > 1 else {})),
         "e2e": {"value": ROWS / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": ROWS * H * 2, "d2h_bytes_per_step": ROWS * H * 2},
-        "gpu_launches": layer.launches_per_step * args.steps,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "how": e2e_note, "result_checked": e2e_equal},
+        "gpu_launches": launches,
+        "parity": parity,
         "roofline": {"bound": "tensor",
                      "kernel": "gemm_tc_kernel<FUSED> (gate/up GEMM + SiLU*mul epilogue + down GEMM, one persistent launch)",
-                     "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                     "achieved": achieved, "peak": burst, "unit": "TFLOP/s", "frac": achieved / burst,
                      "peak_source": f"{peak_kind} cuBLAS bf16 burst", "frac_of_sustained": achieved / sustained,
                      "sustained_peak": sustained,
                      "frac_of_nominal_2250": achieved / 2250.0, "traffic": traffic,
@@ -403,11 +790,79 @@ def run_ours(args) -> None:
         "mlp_pct_tensor_peak": 100.0 * step_flops / (ms_step * 1e-3) / 1e12 / burst,
         "clocks": sampler.summary(t_wall0, t_wall1) if sampler is not None else None,
         "cpu_baseline": cpu,
+        "torch_chain": chain,
+        "decoder": decoder,
         "sweep": sweep,
     }
+    if chain is not None:
+        line["torch_chain"]["fused_kernel_speedup"] = chain["ms_per_step"] / ms_step
     if world > 1:
-        line["comm"] = dict(comm_summary, **(comm_stats or {}))
-    print(json.dumps(line))
+        line["comm"] = dict(layer.comm_summary(), **(comm_stats or {}))
+    return line
+
+
+def run_ours(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    sync = RankSync(world, dev)
+    closers: list = []
+    line, error, learned = None, None, False
+    try:
+        if args.workload == "moe":
+            line = run_moe(args, sync, closers, rank, world, dev)
+        elif args.workload == "decoder":
+            line = decoder_block(args, sync, closers, rank, world, dev, comm_plan_applied(args, world))
+        else:
+            line = measure(args, sync, closers, rank, world, local_rank, dev)
+    except PeerFailed as exc:
+        error, learned = str(exc), True
+    except Exception as exc:  # noqa: BLE001 -- reported after every rank has left together
+        traceback.print_exc()
+        error = f"{type(exc).__name__}: {exc}"
+    # ---- every rank leaves together, whatever happened: tell the others, stop launching, unmap, exit
+    if world > 1:
+        if not learned:
+            try:
+                sync.reduce_max([0.0], fail=error is not None)
+            except PeerFailed as exc:
+                error = error or str(exc)
+        try:
+            torch.cuda.synchronize()
+        except Exception:  # noqa: BLE001
+            traceback.print_exc()
+        sync.reduce_max([0.0], quiet=True)
+    for close in reversed(closers):
+        try:
+            close()
+        except Exception:  # noqa: BLE001
+            traceback.print_exc()
+    if world > 1:
+        sync.reduce_max([0.0], quiet=True)
+        dist.destroy_process_group()
+    if error is not None:
+        print(f"[bench] rank {rank} failed: {error}", file=sys.stderr)
+        sys.exit(1)
+    if rank == 0:
+        print(json.dumps(line))
+
+
+def comm_plan_applied(args, world: int) -> dict:
+    plan = comm_plan(args, world)
+    if world > 1:
+        from dynaflow_b200.comm import set_exclusive_sms
+
+        set_exclusive_sms(plan["exclusive_sms"])
+    return plan
 
 
 def m_sweep(layer, dev, peaks) -> list[dict]:
@@ -424,7 +879,6 @@ def m_sweep(layer, dev, peaks) -> list[dict]:
         half = rows // 2
         x = torch.randn(rows, H, device=dev).bfloat16()
         y = torch.empty(rows, H, dtype=torch.bfloat16, device=dev)
-        hs = [layer.h_views[i][:half] for i in range(2)]
 
         def serial():
             for i in range(2):
@@ -462,124 +916,19 @@ def m_sweep(layer, dev, peaks) -> list[dict]:
         out.append({"rows": rows, "ms_serial": t_serial, "ms_overlapped": t_overlap, "tflops_serial": flops / t_serial / 1e9,
                     "roofline_ms": bound_ms, "frac_of_roofline": bound_ms / min(t_serial, t_overlap),
                     "bound": "tensor" if flops / (float(peaks["bf16_tflops"]) * 1e12) > bytes_min / (float(peaks["hbm_gbs"]) * 1e9) else "hbm"})
-        del hs
     ops.check_status()
     return out
 
 
-def run_decoder(args) -> None:
-    """Second workload (not the default line): Llama-3-8B-shaped decoder prefill, 8 x 2048 ids, two
-    micro-batches, tensor parallel over the launched ranks. value = tokens/s of the whole stack."""
-    import torch
-    import torch.distributed as dist
-
-    from dynaflow_b200 import ops
-    from dynaflow_b200.decoder import DecoderShape, TensorParallelDecoder
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    shape = DecoderShape(layers=args.layers)
-    batch, seq = 8, 2048
-    plan = comm_plan(args, world)
-    if world > 1:
-        from dynaflow_b200.comm import set_exclusive_sms
-
-        set_exclusive_sms(plan["exclusive_sms"])
-    def build_decoder(p):
-        return TensorParallelDecoder(shape, rank=rank, world=world, max_rows=batch * seq // MICRO_BATCHES,
-                                     micro_batches=MICRO_BATCHES, seed=0, device=dev, n_ctas=p["comm_ctas"],
-                                     multicast=p["comm"] == "multicast", gemm_max_ctas=p["gemm_ctas"])
-
-    try:
-        dec = build_decoder(plan)
-    except Exception as exc:  # noqa: BLE001 -- no multicast mapping: the peer-memory reduction instead
-        if plan["comm"] != "multicast" or args.comm == "multicast":
-            raise
-        print(f"[bench] no multicast mapping ({exc}); using the peer-memory reduction", file=sys.stderr)
-        args.comm = "peer"
-        plan = comm_plan(args, world)
-        dec = build_decoder(plan)
-    ids = torch.randint(0, shape.vocab, (batch, seq), generator=torch.Generator().manual_seed(1)).to(dev)
-
-    def timed(**kw):
-        for _ in range(max(2, args.warmup // 2)):
-            dec.forward(ids, **kw)
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        reps = max(3, args.steps // 20)
-        a.record()
-        for _ in range(reps):
-            dec.forward(ids, **kw)
-        b.record()
-        torch.cuda.synchronize()
-        ms = a.elapsed_time(b) / reps
-        if world > 1:
-            t = torch.tensor([ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
-
-    t_all = timed()
-    ops.check_status()
-    line = {"workload": f"Llama-3-8B-shaped decoder prefill, {shape.layers} layers, ids {batch}x{seq}, "
-                        f"{MICRO_BATCHES} micro-batches, tp{world}",
-            "metric": "prefill tokens/sec", "unit": "tokens/s", "n_gpus": world, "ms_per_forward": t_all, "reduction": plan,
-            "value": batch * seq / (t_all * 1e-3)}
-    peaks, kind = measured_peaks()
-    s = shape
-    linear = 2.0 * (s.hidden * (s.heads + 2 * s.kv_heads) * s.head_dim + s.heads * s.head_dim * s.hidden
-                    + 3 * s.hidden * s.intermediate)
-    attn = 4.0 * ((seq + 1) / 2) * s.heads * s.head_dim
-    flops = (linear + attn) * s.layers * batch * seq
-    line["flops_per_forward"] = flops
-    line["tflops_per_gpu"] = flops / world / (t_all * 1e-3) / 1e12
-    line["frac_of_tensor_peak"] = line["tflops_per_gpu"] / float(peaks["bf16_tflops"])
-    line["peak_source"] = f"{kind} cuBLAS bf16 burst"
-    if world > 1:
-        t_compute = timed(skip_comm=True)
-        t_comm = timed(skip_compute=True)
-        payload = 2 * s.layers * batch * seq * s.hidden * 2
-        line["comm"] = {"ms_overlapped": t_all, "ms_compute_only": t_compute, "ms_comm_only": t_comm,
-                        "hidden_frac": 1.0 - (t_all - t_compute) / t_comm,
-                        "wire_ms_at_770": (world - 1) / world * payload / 770e9 * 1e3,
-                        "roofline_ms": max(flops / world / (float(peaks["bf16_tflops"]) * 1e12),
-                                           (world - 1) / world * payload / 770e9) * 1e3}
-        line["frac_of_roofline"] = line["comm"]["roofline_ms"] / t_all
-    if rank == 0:
-        print(json.dumps(line))
-    if world > 1:
-        dist.barrier()
-        torch.cuda.synchronize()
-    dec.close()
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
-
-
-def run_moe(args) -> None:
-    """Third workload (not the default line): Mixtral-shaped top-2 MoE stack, 16384 tokens per step, 8 experts of
+def run_moe(args, sync, closers, rank: int, world: int, dev) -> dict:
+    """Other workload (not the default line): Mixtral-shaped top-2 MoE stack, 16384 tokens per step, 8 experts of
     intermediate 14336, expert parallel over the launched ranks (one rank: all experts local).
     value = tokens/s through `--moe-layers` layers (dispatch / expert / combine each)."""
     import torch
-    import torch.distributed as dist
 
     from dynaflow_b200 import ops
     from dynaflow_b200.moe import ExpertParallelMoE
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     experts, tokens, layers = 8, ROWS, args.moe_layers
     per_rank = tokens // world
     gen = torch.Generator(device=dev).manual_seed(7)      # same weights on every rank; each keeps its experts
@@ -590,8 +939,10 @@ def run_moe(args) -> None:
     stack = []
     for _ in range(layers):
         w = (weight(experts, I, H), weight(experts, I, H), weight(experts, H, I))
-        stack.append(ExpertParallelMoE(H, I, experts, per_rank, rank=rank, world=world, weights=w, slots=1,
-                                       n_ctas=args.comm_ctas or 32, device=dev))
+        moe = ExpertParallelMoE(H, I, experts, per_rank, rank=rank, world=world, weights=w, slots=1,
+                                n_ctas=args.comm_ctas or 32, device=dev)
+        closers.append(moe.close)
+        stack.append(moe)
         del w
     x = torch.randn(per_rank, H, device=dev, generator=gen).bfloat16()
     logits = [torch.randn(per_rank, experts, device=dev, generator=gen).bfloat16() for _ in range(layers)]
@@ -602,21 +953,15 @@ def run_moe(args) -> None:
 
     for _ in range(max(3, args.warmup)):
         step()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
+    sync.barrier()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     reps = max(3, args.steps // 10)
     a.record()
     for _ in range(reps):
         step()
     b.record()
-    torch.cuda.synchronize()
-    ms = a.elapsed_time(b) / reps
-    if world > 1:
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    sync.barrier()
+    ms = sync.max_ms(a.elapsed_time(b) / reps)
     ops.check_status()
     peaks, kind = measured_peaks()
     flops = 2.0 * tokens * 6.0 * H * I * layers               # two experts per token
@@ -628,16 +973,7 @@ def run_moe(args) -> None:
     # load balance of the first layer's routing (ids of all tokens, two experts each)
     counts = torch.bincount(stack[0].ids[0].flatten().to(torch.int64), minlength=experts).double()
     line["tokens_per_expert_max_over_mean"] = float((counts.max() / counts.mean()).item())
-    if rank == 0:
-        print(json.dumps(line))
-    if world > 1:
-        dist.barrier()
-        torch.cuda.synchronize()
-    for layer in stack:
-        layer.close()
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    return line
 
 
 def main() -> None:
@@ -662,12 +998,13 @@ def main() -> None:
                     help="N > 1 chain: keep the residual stream replicated on every rank instead of sharded by rows")
     ap.add_argument("--moe-layers", type=int, default=4, help="moe workload: number of layers")
     ap.add_argument("--workload", choices=["mlp", "decoder", "moe"], default="mlp",
-                    help="mlp: the fused gated-MLP layer step (the benchmark line); decoder: a Llama-3-8B-shaped "
-                         "decoder prefill on the same kernels (reported separately)")
-    ap.add_argument("--layers", type=int, default=32, help="decoder workload: number of layers")
+                    help="mlp: the fused gated-MLP layer step (the benchmark line, which also carries the decoder "
+                         "block); decoder / moe: that workload alone")
+    ap.add_argument("--layers", type=int, default=32, help="decoder: number of layers")
     ap.add_argument("--fused-norm", action="store_true", help="N > 1 chain: one-launch all-reduce+RMSNorm kernel")
     ap.add_argument("--no-sweep", action="store_true", help="skip the M sweep (profiling runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--no-decoder", action="store_true", help="skip the decoder block (profiling runs)")
     args = ap.parse_args()
     if args.rows != ROWS:
         if args.rows <= 0 or args.rows % (MICRO_BATCHES * 8) != 0:
@@ -676,10 +1013,6 @@ def main() -> None:
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference_arm(args)
-    elif args.workload == "decoder":
-        run_decoder(args)
-    elif args.workload == "moe":
-        run_moe(args)
     else:
         run_ours(args)
 

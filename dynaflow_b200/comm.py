@@ -205,6 +205,28 @@ class PeerComm(_Regions):
         self.bytes_reduced += rows * self.hidden * 2
         return self._sums[slot][:rows]
 
+    def _half(self, fn_name: str, slot: int, rows: int) -> None:
+        rc = getattr(self.lib, fn_name)(ctypes.byref(self._plain_views[slot]), self.world, self.max_rows, self.hidden,
+                                        rows, self.n_ctas, self._status_ptr,
+                                        torch.cuda.current_stream(self.device).cuda_stream)
+        if rc != 0:
+            _check(rc, fn_name)
+        self.launches += 1
+
+    def all_gather(self, slot: int, rows: int) -> torch.Tensor:
+        """Every rank has written ITS row slice (``slice_bounds(rows)``) into ``partial(slot, rows)``;
+        afterwards ``result(slot, rows)`` holds all rows on every rank. Current stream."""
+        self._half("df_all_gather_bf16", slot, rows)
+        return self._sums[slot][:rows]
+
+    def reduce_scatter(self, slot: int, rows: int) -> torch.Tensor:
+        """Every rank's ``partial(slot, rows)`` holds ``rows`` rows of contributions; afterwards
+        this rank's slice of ``result(slot, rows)`` holds their sum over ranks (fp32 in rank order,
+        rounded once). Returns that slice. Current stream."""
+        self._half("df_reduce_scatter_bf16", slot, rows)
+        lo, hi = self.slice_bounds(rows)
+        return self._sums[slot][lo:hi]
+
     def slice_bounds(self, rows: int) -> tuple[int, int]:
         """Rows of a ``rows``-row message that this rank owns."""
         return rows * self.rank // self.world, rows * (self.rank + 1) // self.world
@@ -278,7 +300,13 @@ class MulticastComm(PeerComm):
                 "n_ctas": self.n_ctas, "launches": self.launches, "payload_bytes": self.bytes_reduced}
 
     def close(self) -> None:
+        """Collective: every rank must call it, with none of its kernels in flight; the ranks meet
+        at a barrier before any of them releases its binding to the multicast object."""
+        import torch.distributed as dist
+
         torch.cuda.synchronize(self.device)
+        if self.world > 1 and dist.is_initialized():
+            dist.barrier()
         self._partials, self._sums = [], []
         self.local, self.regions, self.multicast = [], [], []
         self._handle = None

@@ -154,6 +154,20 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
       : "memory");
 }
 
+// The same with the A operand in tensor memory: row i of A in lane i, two consecutive bf16
+// elements of the row per 32-bit column (a K step of 16 elements = 8 columns).
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // The mbarrier receives one arrival once every MMA issued so far by this
 // thread has finished reading shared memory and writing tensor memory.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {

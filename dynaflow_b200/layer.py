@@ -259,6 +259,64 @@ class TensorParallelGatedMLP:
         for done in joins:
             main.wait_event(done)
 
+    def forward_host_sliced(self, x_host_local: torch.Tensor, out_host_local: torch.Tensor, cuts: list[int],
+                            comm_in: Any) -> None:
+        """The host-staged step at ``world > 1`` without replicated copies: of every micro-batch
+        ``[cuts[i], cuts[i+1])`` this rank owns the row slice ``comm.slice_bounds(rows)``;
+        ``x_host_local`` / ``out_host_local`` (pinned) hold this rank's slices of all micro-batches
+        back to back. Per micro-batch, on its own stream: copy the slice in, all-gather the
+        micro-batch over NVLink (``comm_in``, a second communicator for the input rows), run the
+        GEMMs on all rows, reduce-scatter the partial outputs, copy the owned rows out. Host
+        traffic per rank and step is ``2 * rows * hidden * 2 / world`` bytes. The collectives of all
+        micro-batches go through the one communication stream, in the same order on every rank."""
+        assert self.world > 1 and self.comm is not None
+        main = torch.cuda.current_stream(self.device)
+        cs = self.comm.stream
+        plan = []
+        base = 0
+        for mb in range(len(cuts) - 1):
+            rows = cuts[mb + 1] - cuts[mb]
+            if rows == 0:
+                continue
+            lo, hi = self.comm.slice_bounds(rows)
+            plan.append((mb % self.micro_batches, rows, lo, hi, base))
+            base += hi - lo
+        # first the copies in and the all-gathers of every micro-batch, then the GEMMs: the second
+        # micro-batch's rows arrive under the first one's GEMMs
+        gathered = []
+        for slot, rows, lo, hi, at in plan:
+            stream = self.streams[slot]
+            with torch.cuda.stream(stream):
+                comm_in.partial(slot, rows)[lo:hi].copy_(x_host_local[at:at + hi - lo], non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(stream)
+            cs.wait_event(ready)
+            with torch.cuda.stream(cs):
+                x_all = comm_in.all_gather(slot, rows)
+                ev = torch.cuda.Event()
+                ev.record(cs)
+            gathered.append((x_all, ev))
+        joins = []
+        for (slot, rows, lo, hi, at), (x_all, ev) in zip(plan, gathered):
+            stream = self.streams[slot]
+            with torch.cuda.stream(stream):
+                stream.wait_event(ev)
+                self._mlp(x_all, self.comm.partial(slot, rows), slot, False)
+                done = torch.cuda.Event()
+                done.record(stream)
+                cs.wait_event(done)
+                with torch.cuda.stream(cs):
+                    y_mine = self.comm.reduce_scatter(slot, rows)
+                    reduced = torch.cuda.Event()
+                    reduced.record(cs)
+                stream.wait_event(reduced)
+                out_host_local[at:at + hi - lo].copy_(y_mine, non_blocking=True)
+                out_done = torch.cuda.Event()
+                out_done.record(stream)
+                joins.append(out_done)
+        for ev in joins:
+            main.wait_event(ev)
+
     def comm_summary(self) -> dict:
         return self.comm.summary() if self.comm is not None else {}
 

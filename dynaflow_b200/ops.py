@@ -229,6 +229,55 @@ def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: to
     return out
 
 
+def attention_decode_workspace_bytes(batch: int, q_heads: int, kv_heads: int, max_len: int) -> int:
+    return int(_native.load().df_attention_decode_workspace_bytes(batch, q_heads, kv_heads, max_len))
+
+
+def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_lens: torch.Tensor,
+                     out: torch.Tensor, workspace: torch.Tensor, *, scale: float | None = None,
+                     max_ctas: int = 0) -> torch.Tensor:
+    """One new token per sequence against its key/value cache. ``q, out [B, Hq*128]`` (2-D bf16
+    views, unit inner stride), ``k_cache, v_cache [B, max_len, Hkv*128]`` contiguous bf16 with the
+    rows beyond ``seq_lens[b]`` finite, ``seq_lens`` int32 on the device, ``workspace`` a uint8
+    tensor of ``attention_decode_workspace_bytes`` bytes."""
+    _require_bf16_2d("q", q)
+    _require_bf16_2d("out", out)
+    hd = 128
+    B = q.shape[0]
+    if k_cache.dtype != torch.bfloat16 or k_cache.dim() != 3 or not k_cache.is_contiguous() \
+            or tuple(v_cache.shape) != tuple(k_cache.shape) or not v_cache.is_contiguous() or k_cache.shape[0] != B:
+        raise ValueError("expected contiguous bf16 caches [B, max_len, Hkv*128]")
+    max_len, kv_cols = k_cache.shape[1], k_cache.shape[2]
+    if q.shape[1] % hd or kv_cols % hd or tuple(out.shape) != tuple(q.shape):
+        raise ValueError("expected q/out [B, Hq*128] and caches [B, max_len, Hkv*128]")
+    if seq_lens.dtype != torch.int32 or not seq_lens.is_cuda or seq_lens.numel() != B:
+        raise ValueError("seq_lens must be an int32 device tensor of B entries")
+    _dev_index(q)
+    st = status_block(q.device)
+    rc = _native.load().df_attention_decode_bf16(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), seq_lens.data_ptr(), B, max_len,
+        q.shape[1] // hd, kv_cols // hd, hd, q.stride(0), kv_cols, out.stride(0),
+        float(scale if scale is not None else hd ** -0.5), workspace.data_ptr(), workspace.numel(), max_ctas,
+        st.data_ptr(), _stream_ptr(q))
+    _check(rc, "df_attention_decode_bf16")
+    return out
+
+
+def kv_cache_append(k_new: torch.Tensor, v_new: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    seq_lens: torch.Tensor) -> None:
+    """``cache[b, seq_lens[b] - 1] = new[b]`` for keys and values (``k_new, v_new [B, Hkv*128]`` views
+    with equal row strides)."""
+    _require_bf16_2d("k_new", k_new)
+    _require_bf16_2d("v_new", v_new)
+    if k_new.stride(0) != v_new.stride(0) or tuple(k_new.shape) != tuple(v_new.shape):
+        raise ValueError("k_new and v_new must have equal shapes and row strides")
+    B, cols = k_new.shape
+    rc = _native.load().df_kv_cache_append_bf16(k_new.data_ptr(), v_new.data_ptr(), k_new.stride(0), k_cache.data_ptr(),
+                                                v_cache.data_ptr(), cols, seq_lens.data_ptr(), B, k_cache.shape[1],
+                                                cols // 128, 128, _stream_ptr(k_new))
+    _check(rc, "df_kv_cache_append_bf16")
+
+
 STATIC_SCRATCH_BYTES = 64 << 20
 
 

@@ -324,6 +324,33 @@ int df_attention_prefill_bf16(const void* q, const void* k, const void* v, void*
                               int ld_q, int ld_k, int ld_v, int ld_out, float scale, int max_ctas,
                               df_status_t* dev_status, void* stream);
 
+/* Attention of a decode step: one new token per sequence against a key/value cache (the same
+ * opaque `attention` subgraph, in the decode phase the reference captures into CUDA graphs per
+ * nano-batch: dynaflow/executor/cudagraph.py:84-123).
+ *   q        [batch, q_heads * 128] bf16, row stride ld_q (a column range of the fused qkv rows)
+ *   k_cache, v_cache  [batch, max_len, kv_heads * 128] bf16, row stride ld_kv elements: sequence b
+ *            owns rows [b * max_len, (b + 1) * max_len), of which the first seq_lens_dev[b] are valid
+ *            (the new token's key and value included: see df_kv_cache_append_bf16). Rows of the
+ *            cache that are not valid are read but masked: they must hold finite values
+ *            (allocate the cache zeroed)
+ *   out      [batch, q_heads * 128] bf16
+ * The keys of a sequence are cut into chunks that different CTAs process (split-KV); `workspace`
+ * (df_attention_decode_workspace_bytes, 16-byte aligned, contents arbitrary) receives the chunks'
+ * partial results, which a second small launch merges. seq_lens_dev stays in device memory, so a
+ * captured graph follows growing sequences. head_dim must be 128, q_heads / kv_heads <= 32. */
+size_t df_attention_decode_workspace_bytes(int batch, int q_heads, int kv_heads, int max_len);
+int df_attention_decode_bf16(const void* q, const void* k_cache, const void* v_cache, void* out,
+                             const int* seq_lens_dev, int batch, int max_len, int q_heads, int kv_heads,
+                             int head_dim, int ld_q, int ld_kv, int ld_out, float scale, void* workspace,
+                             size_t workspace_bytes, int max_ctas, df_status_t* dev_status, void* stream);
+
+/* cache[b, seq_lens_dev[b] - 1, :] = new[b, :] for keys and values: the new token of every
+ * sequence takes the last valid position of its cache (k_new / v_new: [batch, kv_heads * head_dim]
+ * with row stride ld_new, e.g. column ranges of the fused qkv rows after df_rope_bf16). */
+int df_kv_cache_append_bf16(const void* k_new, const void* v_new, int ld_new, void* k_cache, void* v_cache,
+                            int ld_cache, const int* seq_lens_dev, int batch, int max_len, int kv_heads,
+                            int head_dim, void* stream);
+
 /* Size of the library-owned scratch behind df_mlp_gated_bf16_static: 64 MiB of
  * static device memory, held by every GPU that loads the library until the
  * process exits. */

@@ -120,3 +120,22 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seq_lens
         start += n
     assert start == T
     return out
+
+
+def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_lens: list[int],
+                     scale: float | None = None) -> torch.Tensor:
+    """One query token per sequence against its key/value cache. ``q [B, Hq, D]``,
+    ``k_cache, v_cache [B, max_len, Hkv, D]`` of which the first ``seq_lens[b]`` positions are
+    valid -> ``[B, Hq, D]``. Same statement as ``causal_attention`` for the last position of a
+    sequence (the new token attends to every valid key, itself included)."""
+    B, hq, d = q.shape
+    hkv = k_cache.shape[2]
+    scale = scale if scale is not None else d ** -0.5
+    out = torch.empty_like(q)
+    for b, n in enumerate(seq_lens):
+        ks = k_cache[b, :n].float().transpose(0, 1).repeat_interleave(hq // hkv, dim=0)     # [Hq, n, D]
+        vs = v_cache[b, :n].float().transpose(0, 1).repeat_interleave(hq // hkv, dim=0)
+        s = torch.einsum("hd,hnd->hn", q[b].float(), ks) * scale
+        p = torch.softmax(s, dim=-1).to(q.dtype).float()
+        out[b] = torch.einsum("hn,hnd->hd", p, vs).to(q.dtype)
+    return out

@@ -8,7 +8,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 GOLDEN = os.path.join(ROOT, "tests", "golden")
-REFERENCE = "/root/reference"
+REFERENCE = os.environ.get("DYNAFLOW_REFERENCE", "/root/reference")
 
 
 def pytest_configure(config):

@@ -104,3 +104,58 @@ def test_rejects_unsupported_head_dim(native_lib):
     rc = native_lib.df_attention_prefill_bf16(x.data_ptr(), x.data_ptr(), x.data_ptr(), x.data_ptr(), 128, 1, 128, None, 1, 1,
                                               64, 64, 64, 64, 64, 0.125, 0, st.data_ptr(), None)
     assert rc == -3
+
+
+# ------------------------------------------------------------------ decode (split-KV)
+def _decode_case(ops, batch, max_len, hq, hkv, lens, seed, max_ctas=0):
+    from oracle import ops_oracle
+
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(batch, hq * HD, generator=g).bfloat16()
+    kc = torch.randn(batch, max_len, hkv * HD, generator=g).bfloat16()
+    vc = torch.randn(batch, max_len, hkv * HD, generator=g).bfloat16()
+    out = torch.full((batch, hq * HD), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ws = torch.empty(ops.attention_decode_workspace_bytes(batch, hq, hkv, max_len), dtype=torch.uint8, device="cuda")
+    sl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    ops.attention_decode(q.cuda(), kc.cuda(), vc.cuda(), sl, out, ws, max_ctas=max_ctas)
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = ops_oracle.decode_attention(q.view(batch, hq, HD), kc.view(batch, max_len, hkv, HD),
+                                       vc.view(batch, max_len, hkv, HD), lens).reshape(batch, hq * HD)
+    return out.cpu(), want
+
+
+@pytest.mark.parametrize("batch,max_len,hq,hkv,lens", [
+    (1, 128, 4, 1, [128]), (2, 256, 4, 1, [1, 256]), (3, 640, 8, 2, [640, 129, 300]), (5, 1024, 4, 4, [7, 1000, 512, 513, 1]),
+    (4, 4096, 4, 1, [4096, 4095, 2049, 100])])
+def test_decode_attention_matches_oracle(ops, batch, max_len, hq, hkv, lens):
+    got, want = _decode_case(ops, batch, max_len, hq, hkv, lens, 31)
+    assert torch.isfinite(got.float()).all()
+    assert _rel(got, want) <= TOL
+
+
+def test_decode_attention_on_few_ctas_is_within_tolerance(ops):
+    """Fewer CTAs cut the cache into fewer, longer chunks: another summation order, same result
+    within tolerance."""
+    lens = [900, 1024, 333, 64, 1, 512]
+    a, want = _decode_case(ops, 6, 1024, 8, 2, lens, 32)
+    b, _ = _decode_case(ops, 6, 1024, 8, 2, lens, 32, max_ctas=3)
+    assert _rel(a, want) <= TOL and _rel(b, want) <= TOL
+
+
+def test_kv_cache_append_writes_the_last_valid_position(ops):
+    g = torch.Generator().manual_seed(33)
+    B, max_len, cols = 5, 40, 2 * HD
+    qkv = torch.randn(B, 6 * HD, generator=g).bfloat16().cuda()
+    kc = torch.zeros(B, max_len, cols, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    lens = [1, 40, 17, 2, 33]
+    sl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    k_new, v_new = qkv[:, 2 * HD:4 * HD], qkv[:, 4 * HD:]
+    ops.kv_cache_append(k_new, v_new, kc, vc, sl)
+    torch.cuda.synchronize()
+    for b, n in enumerate(lens):
+        assert torch.equal(kc[b, n - 1], k_new[b]) and torch.equal(vc[b, n - 1], v_new[b])
+        keep = torch.ones(max_len, dtype=torch.bool)
+        keep[n - 1] = False
+        assert kc[b, keep].abs().sum() == 0 and vc[b, keep].abs().sum() == 0
