@@ -569,6 +569,68 @@ def decoder_block(args, sync, closers, rank: int, world: int, dev, plan: dict) -
     return out
 
 
+def decode_block(args, sync, closers, rank: int, world: int, dev, plan: dict) -> dict:
+    """Llama-3-8B-shaped decoder in DECODE: batch 256, one new token per sequence, key/value cache of
+    4096 positions per sequence filled N(0,1), two micro-batches of 128, tensor parallel over the
+    ranks, the whole step (every kernel and reduction of both streams) replayed as ONE CUDA graph.
+    The step is bound by streaming weights and cache from HBM: tokens/s against that bound."""
+    import torch
+
+    from dynaflow_b200 import ops
+    from dynaflow_b200.decoder import DecoderShape, TensorParallelDecoder
+
+    shape = DecoderShape(layers=args.layers)
+    batch, kv_len = args.decode_batch, args.kv_len
+    dec = TensorParallelDecoder(shape, rank=rank, world=world, max_rows=batch // MICRO_BATCHES,
+                                micro_batches=MICRO_BATCHES, seed=0, device=dev, n_ctas=max(plan["comm_ctas"], 1),
+                                multicast=plan["comm"] == "multicast", gemm_max_ctas=plan["gemm_ctas"])
+    closers.append(dec.close)
+    dec.init_decode(batch, kv_len, context_len=kv_len, fill_seed=2)
+    ids = torch.randint(0, shape.vocab, (batch,), generator=torch.Generator().manual_seed(3)).to(dev)
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        sync.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        sync.barrier()
+        return sync.max_ms(a.elapsed_time(b) / reps)
+
+    t_eager = timed(lambda: dec.decode_step(ids), 3)
+    ops.check_status()
+    replay, logits = dec.capture_decode(ids)
+    t_graph = timed(replay, max(10, args.steps // 4))
+    ops.check_status()
+    identical = sync.all_equal(digest_of(torch.cat(dec.last_hidden)))
+    finite = bool(torch.isfinite(torch.cat(logits).float()).all().item())
+    peaks, kind = measured_peaks()
+    weight_bytes = sum(t.numel() * 2 for layer in dec.layers for k, t in layer.items() if k.startswith("w"))
+    weight_bytes += dec.lm_head_shard.numel() * 2
+    kv_bytes = 2 * shape.layers * batch * kv_len * dec.kv_cols * 2
+    total = weight_bytes + kv_bytes
+    hbm = float(peaks["hbm_gbs"]) * 1e9
+    out = {"workload": f"Llama-3-8B-shaped decode, {shape.layers} layers, batch {batch}, cache {kv_len} per sequence, "
+                       f"{MICRO_BATCHES} micro-batches, tp{world}, one CUDA graph per step",
+           "tokens_per_s": batch / (t_graph * 1e-3), "ms_per_step_graph": t_graph, "ms_per_step_eager_dispatch": t_eager,
+           "hbm_bytes_per_step_per_gpu": total, "weights_bytes": weight_bytes, "kv_cache_bytes": kv_bytes,
+           "achieved_gbs": total / (t_graph * 1e-3) / 1e9, "hbm_peak_gbs": float(peaks["hbm_gbs"]),
+           "frac_of_hbm_roofline": total / hbm / (t_graph * 1e-3), "bound_tokens_per_s": batch / (total / hbm),
+           "peak_source": f"{kind} copy bandwidth", "ranks_identical": bool(identical), "logits_finite": finite}
+    if world > 1:
+        replay_nc, _ = dec.capture_decode(ids, skip_comm=True)
+        t_compute = timed(replay_nc, 10)
+        replay_cc, _ = dec.capture_decode(ids, skip_compute=True)
+        t_comm = timed(replay_cc, 10)
+        out.update({"ms_compute_only": t_compute, "ms_comm_only": t_comm,
+                    "hidden_frac": 1.0 - (t_graph - t_compute) / t_comm})
+    ops.check_status()
+    return out
+
+
 def measure(args, sync, closers, rank: int, world: int, local_rank: int, dev) -> dict:
     import torch
 
@@ -676,9 +738,10 @@ def measure(args, sync, closers, rank: int, world: int, local_rank: int, dev) ->
             sync.barrier()
             return sync.max_ms(a.elapsed_time(b) / reps / chain_layers)
 
+        # all three measured the same way (short bursts at the same clocks); `value` keeps the long timed region
+        t_overlap = timed()
         t_compute = timed(skip_comm=True)
         t_comm = timed(skip_compute=True)
-        t_overlap = ms_step
         payload = ROWS * H * 2  # bytes reduced per block (all micro-batches)
         peak_tf = float(measured_peaks()[0]["bf16_tflops"])
         comm_stats = {"chain": "dependent TP MLP blocks; between them all-reduce + residual + RMSNorm: "
@@ -745,10 +808,12 @@ def measure(args, sync, closers, rank: int, world: int, local_rank: int, dev) ->
         sampler.stop()
 
     chain = torch_chain_ms(layer, x_dev, cuts, args.steps) if world == 1 else None
-    decoder = None
+    decoder = decode = None
     if not args.no_decoder:
-        # free the MLP layer's activations first; the decoder brings its own buffers and communicator
         decoder = decoder_block(args, sync, closers, rank, world, dev, plan)
+        if world > 1:
+            # (one GPU cannot hold the full key/value cache of this configuration beside the other workloads)
+            decode = decode_block(args, sync, closers, rank, world, dev, plan)
 
     peaks, peak_kind = measured_peaks()
     rows_mb = ROWS // MICRO_BATCHES
@@ -792,6 +857,7 @@ def measure(args, sync, closers, rank: int, world: int, local_rank: int, dev) ->
         "cpu_baseline": cpu,
         "torch_chain": chain,
         "decoder": decoder,
+        "decode": decode,
         "sweep": sweep,
     }
     if chain is not None:
@@ -822,6 +888,8 @@ def run_ours(args) -> None:
             line = run_moe(args, sync, closers, rank, world, dev)
         elif args.workload == "decoder":
             line = decoder_block(args, sync, closers, rank, world, dev, comm_plan_applied(args, world))
+        elif args.workload == "decode":
+            line = decode_block(args, sync, closers, rank, world, dev, comm_plan_applied(args, world))
         else:
             line = measure(args, sync, closers, rank, world, local_rank, dev)
     except PeerFailed as exc:
@@ -997,7 +1065,9 @@ def main() -> None:
     ap.add_argument("--replicated-residual", action="store_true",
                     help="N > 1 chain: keep the residual stream replicated on every rank instead of sharded by rows")
     ap.add_argument("--moe-layers", type=int, default=4, help="moe workload: number of layers")
-    ap.add_argument("--workload", choices=["mlp", "decoder", "moe"], default="mlp",
+    ap.add_argument("--decode-batch", type=int, default=256, help="decode: sequences per step")
+    ap.add_argument("--kv-len", type=int, default=4096, help="decode: cached positions per sequence")
+    ap.add_argument("--workload", choices=["mlp", "decoder", "decode", "moe"], default="mlp",
                     help="mlp: the fused gated-MLP layer step (the benchmark line, which also carries the decoder "
                          "block); decoder / moe: that workload alone")
     ap.add_argument("--layers", type=int, default=32, help="decoder: number of layers")

@@ -208,6 +208,146 @@ class TensorParallelDecoder:
             main.wait_stream(comm_stream)
         return torch.cat([xs[mb] for mb in range(n)], 0)
 
+    # ------------------------------------------------------------------ decode
+    def init_decode(self, batch: int, max_len: int, context_len: int, fill_seed: int | None = 0) -> None:
+        """Allocates what a decode step needs: per layer a key and a value cache
+        ``[batch, max_len, kv_cols]`` (this rank's key/value heads), filled N(0, 1) from
+        ``fill_seed`` (``None``: zeros), the sequence lengths (every sequence holds ``context_len``
+        keys AFTER the new token has been appended), and the split-KV workspace."""
+        s, dev = self.s, self.device
+        n = min(self.micro_batches, batch)
+        self.d_batch, self.d_max_len = batch, max_len
+        self.d_cuts = [batch * i // n for i in range(n + 1)]
+        gen = torch.Generator(device=dev).manual_seed(fill_seed if fill_seed is not None else 0)
+        shape = (s.layers, batch, max_len, self.kv_cols)
+        if fill_seed is None:
+            self.k_cache = torch.zeros(shape, dtype=torch.bfloat16, device=dev)
+            self.v_cache = torch.zeros(shape, dtype=torch.bfloat16, device=dev)
+        else:
+            self.k_cache = torch.empty(shape, dtype=torch.bfloat16, device=dev)
+            self.v_cache = torch.empty(shape, dtype=torch.bfloat16, device=dev)
+            for li in range(s.layers):           # layer by layer: no fp32 copy of the whole cache
+                self.k_cache[li].copy_(torch.randn(shape[1:], generator=gen, device=dev))
+                self.v_cache[li].copy_(torch.randn(shape[1:], generator=gen, device=dev))
+        self.seq_lens = torch.full((batch,), context_len, dtype=torch.int32, device=dev)
+        self.positions = self.seq_lens - 1
+        rows = max(self.d_cuts[i + 1] - self.d_cuts[i] for i in range(n))
+        ws = ops.attention_decode_workspace_bytes(rows, self.qh, self.kvh, max_len)
+        self.attn_ws = [torch.empty(ws, dtype=torch.uint8, device=dev) for _ in range(n)]
+        per = s.vocab // self.world
+        self.lm_head_shard = self.lm_head[self.rank * per:(self.rank + 1) * per].contiguous()
+        self.logits = [torch.empty(rows, per, dtype=torch.bfloat16, device=dev) for _ in range(n)]
+
+    def _attention_half_decode(self, li: int, layer: dict, x: torch.Tensor, mb: int) -> None:
+        """qkv projection, RoPE at the sequences' last positions, the new keys and values into the
+        cache, split-KV attention over the cache, output projection into the partial buffer."""
+        s = self.s
+        lo, hi = self.d_cuts[mb], self.d_cuts[mb + 1]
+        rows = hi - lo
+        qkv = self.qkv[mb][:rows]
+        ops.gemm_bf16(x, layer["wqkv"], out=qkv, max_ctas=self.gemm_max_ctas)
+        rc = self.lib.df_rope_bf16(qkv.data_ptr(), self.positions[lo:hi].data_ptr(), rows, self.qh + self.kvh, s.head_dim,
+                                   qkv.stride(0), s.rope_theta, torch.cuda.current_stream(self.device).cuda_stream)
+        if rc != 0:
+            raise RuntimeError(_native.last_error())
+        k_new = qkv[:, self.q_cols:self.q_cols + self.kv_cols]
+        v_new = qkv[:, self.q_cols + self.kv_cols:]
+        kc, vc = self.k_cache[li, lo:hi], self.v_cache[li, lo:hi]
+        ops.kv_cache_append(k_new, v_new, kc, vc, self.seq_lens[lo:hi])
+        attn = self.attn_out[mb][:rows]
+        ops.attention_decode(qkv[:, :self.q_cols], kc, vc, self.seq_lens[lo:hi], attn, self.attn_ws[mb],
+                             max_ctas=self.gemm_max_ctas)
+        ops.gemm_bf16(attn, layer["wo"], out=self._partial(mb, rows), max_ctas=self.gemm_max_ctas)
+        self.launch_count += 6
+
+    def decode_step(self, ids: torch.Tensor, skip_comm: bool = False, skip_compute: bool = False) -> list[torch.Tensor]:
+        """One new token per sequence: ``ids [batch]`` -> per micro-batch this rank's slice of the
+        logits ``[rows, vocab / world]``. Same schedule as ``forward``: the micro-batches' compute on
+        the current stream, the reduction of micro-batch i on the communication stream under the
+        kernels of micro-batch i+1 (attention of one under the reduction of the other). Allocates
+        nothing and never synchronises with the host, so it can be captured into one CUDA graph
+        (``capture_decode``); the sequence lengths stay in device memory."""
+        n = len(self.d_cuts) - 1
+        main = torch.cuda.current_stream(self.device)
+        comm_stream = self.comm.stream if self.comm is not None else main
+        xs: list = [None] * n
+        rows_of = [self.d_cuts[i + 1] - self.d_cuts[i] for i in range(n)]
+        torch.sub(self.seq_lens, 1, out=self.positions)
+        for mb in range(n):
+            target = self.partial_local[mb][:rows_of[mb]] if self.comm is None else self.comm.partial(mb, rows_of[mb])
+            torch.index_select(self.embed, 0, ids[self.d_cuts[mb]:self.d_cuts[mb + 1]], out=target)
+            if self.comm is not None:
+                target.mul_(1.0 / self.world)
+        if self.comm is not None:
+            start = torch.cuda.Event()
+            start.record(main)
+            comm_stream.wait_event(start)
+        done: list = [None] * n
+
+        def reduce_after(mb: int, weight: torch.Tensor, first: bool = False) -> None:
+            rows = rows_of[mb]
+            if self.comm is None:
+                xs[mb] = self._reduce_norm(mb, rows, weight, first)
+                return
+            ready = torch.cuda.Event()
+            ready.record(main)
+            if skip_comm:
+                xs[mb] = self.comm.partial(mb, rows)
+                return
+            comm_stream.wait_event(ready)
+            with torch.cuda.stream(comm_stream):
+                xs[mb] = self._reduce_norm(mb, rows, weight, first)
+                ev = torch.cuda.Event()
+                ev.record(comm_stream)
+            done[mb] = ev
+
+        for mb in range(n):
+            reduce_after(mb, self.layers[0]["norm1"], first=True)
+        for li, layer in enumerate(self.layers):
+            for mb in range(n):
+                if done[mb] is not None:
+                    main.wait_event(done[mb])
+                if not skip_compute:
+                    self._attention_half_decode(li, layer, xs[mb], mb)
+                reduce_after(mb, layer["norm2"])
+            nxt = self.layers[li + 1]["norm1"] if li + 1 < len(self.layers) else self.final_norm
+            for mb in range(n):
+                if done[mb] is not None:
+                    main.wait_event(done[mb])
+                if not skip_compute:
+                    self._mlp_half(layer, xs[mb], mb, rows_of[mb])
+                reduce_after(mb, nxt)
+        out = []
+        for mb in range(n):
+            if done[mb] is not None:
+                main.wait_event(done[mb])
+            lg = self.logits[mb][:rows_of[mb]]
+            if not skip_compute:
+                ops.gemm_bf16(xs[mb], self.lm_head_shard, out=lg, max_ctas=self.gemm_max_ctas)
+            out.append(lg)
+        if self.comm is not None:
+            main.wait_stream(comm_stream)
+        self.last_hidden = xs
+        return out
+
+    def capture_decode(self, ids: torch.Tensor, **kw):
+        """Runs one decode step eagerly (kernels loaded, workspaces created), then captures the step
+        -- both streams, every kernel and reduction -- into ONE CUDA graph. Returns
+        ``(replay, logits)``: ``replay()`` launches the graph on the current stream; ``ids`` is
+        read at replay time from the tensor passed here, the sequence lengths from
+        ``self.seq_lens``."""
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):          # the eager run on the capture stream: its scratch is created here
+            self.decode_step(ids, **kw)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side, capture_error_mode="thread_local"):
+                logits = self.decode_step(ids, **kw)
+        torch.cuda.current_stream(self.device).wait_stream(side)
+        return graph.replay, logits
+
     def logits_last_token(self, hidden: torch.Tensor, batch: int, seq: int) -> torch.Tensor:
         """Prefill only needs the logits of each request's last token."""
         last = hidden.view(batch, seq, -1)[:, -1, :].contiguous()

@@ -86,3 +86,54 @@ def test_rope_kernel_matches_rotate_half(native_lib):
     assert torch.equal(got[:, heads * hd:], x[:, heads * hd:])
     rel = ((got[:, :heads * hd].float() - want.float()).abs().max() / want.float().abs().max()).item()
     assert rel <= 1e-2
+
+
+def test_decode_step_matches_pytorch_decoder(native_lib):
+    """One decode step (new token against a key/value cache, two micro-batches) on the native kernels,
+    eagerly and replayed from one CUDA graph, against the PyTorch decoder run over the whole sequences:
+    the cache is filled with the oracle's own rotated keys and values of the earlier positions."""
+    from dynaflow_b200 import ops
+    from dynaflow_b200.decoder import DecoderShape, TensorParallelDecoder, reference_weights
+    from oracle import llama_oracle
+
+    shape = DecoderShape(hidden=256, intermediate=512, heads=4, kv_heads=2, head_dim=128, layers=2, vocab=512)
+    weights = reference_weights(shape, seed=14)
+    B, L, max_len = 6, 150, 200
+    ids = torch.randint(0, shape.vocab, (B, L), generator=torch.Generator().manual_seed(15)).cuda()
+    model = load_oracle_model(shape, weights).cuda()
+    keys, values = [], []
+    with torch.inference_mode():
+        cos, sin = llama_oracle.rope_tables(L, shape.head_dim, shape.rope_theta, device=ids.device)
+        x = model.embed(ids)
+        for blk in model.blocks:
+            h = blk.input_norm(x)
+            k = blk.attn.k_proj(h).view(B, L, shape.kv_heads, shape.head_dim).transpose(1, 2)
+            v = blk.attn.v_proj(h).view(B, L, shape.kv_heads, shape.head_dim).transpose(1, 2)
+            keys.append(llama_oracle.apply_rope(k, cos, sin).transpose(1, 2).reshape(B, L, -1))
+            values.append(v.transpose(1, 2).reshape(B, L, -1))
+            x = blk(x, cos, sin)
+        want = model.lm_head(model.norm(x)[:, -1])
+    dec = TensorParallelDecoder(shape, max_rows=B, micro_batches=2, weights=weights)
+    dec.init_decode(B, max_len, context_len=L, fill_seed=None)
+    for li in range(shape.layers):
+        dec.k_cache[li, :, :L - 1].copy_(keys[li][:, :L - 1])
+        dec.v_cache[li, :, :L - 1].copy_(values[li][:, :L - 1])
+    last = ids[:, -1].contiguous()
+    got = torch.cat(dec.decode_step(last)).clone()
+    torch.cuda.synchronize()
+    ops.check_status()
+    rel = ((got.float() - want.float()).abs().max() / want.float().abs().max()).item()
+    assert got.shape == want.shape and rel <= TOL, rel
+    # the step wrote the new token's keys and values where the oracle has them
+    assert ((dec.k_cache[0, :, L - 1].float() - keys[0][:, L - 1].float()).abs().max()
+            / keys[0].float().abs().max()).item() <= TOL
+    # the same step as one CUDA graph, replayed twice
+    replay, logits = dec.capture_decode(last)
+    for _ in range(2):
+        for lg in logits:
+            lg.zero_()
+        replay()
+        torch.cuda.synchronize()
+        ops.check_status()
+        again = torch.cat(logits)
+        assert torch.equal(again, got)
