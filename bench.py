@@ -761,49 +761,104 @@ def measure(args, sync, closers, rank: int, world: int, local_rank: int, dev) ->
         comm_stats["frac_of_roofline_chain"] = comm_stats["roofline_ms_per_block"] / t_overlap
         ops.check_status()
 
-    # ---- end to end: pinned host buffers, copies inside the timed region
+    # ---- end to end: pinned host buffers, copies inside the timed region, the step driven through the drop-in API
+    #      (DynaFlowManager.get_callable(): policy, nano-batch dispatch, native substitution of the MLP subgraph, the
+    #      collectives as network-tagged subgraphs, whole-forward graph). Every rank owns 1/N of the rows of each
+    #      micro-batch and copies only those in and out; copy-in, step and copy-out of consecutive steps ride on three
+    #      streams with two buffers each.
+    from dynaflow_b200.host_step import ManagedLayerStep
+
     if world == 1:
-        def e2e_step():
-            layer.forward_host(x_host, out_host, cuts)
-
-        h2d = d2h = ROWS * H * 2
-        e2e_note = "pinned host X -> H2D -> MLP -> D2H per micro-batch on its own stream (C ABI through TensorParallelGatedMLP)"
+        sizes = [(0, cuts[i + 1] - cuts[i]) for i in range(MICRO_BATCHES)]
     else:
-        # every rank owns 1/N of the rows of each micro-batch: it copies only those in and out
         sizes = [comm.slice_bounds(cuts[i + 1] - cuts[i]) for i in range(MICRO_BATCHES)]
-        local = sum(hi - lo for lo, hi in sizes)
-        xl = torch.cat([x_host[cuts[i] + lo: cuts[i] + hi] for i, (lo, hi) in enumerate(sizes)]).pin_memory()
-        ol = torch.empty(local, H, dtype=torch.bfloat16).pin_memory()
+    local = sum(hi - lo for lo, hi in sizes)
+    cuts_local = [0]
+    for lo, hi in sizes:
+        cuts_local.append(cuts_local[-1] + hi - lo)
+    xl = torch.cat([x_host[cuts[i] + lo: cuts[i] + hi] for i, (lo, hi) in enumerate(sizes)]).pin_memory()
+    ol = torch.empty(local, H, dtype=torch.bfloat16).pin_memory()
+    managed = ManagedLayerStep(layer, comm_in=comm_in, whole_forward_graph=True)
+    main = torch.cuda.current_stream(dev)
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    x_bufs = [torch.empty(local, H, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    o_bufs = [torch.empty(local, H, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    arrived = [torch.cuda.Event() for _ in range(2)]
+    ready = [torch.cuda.Event() for _ in range(2)]
+    drained = [torch.cuda.Event() for _ in range(2)]
+    for ev in consumed + drained:
+        ev.record(main)
+    step_no = [0]
 
-        def e2e_step():
-            layer.forward_host_sliced(xl, ol, cuts, comm_in)
+    def e2e_step():
+        k = step_no[0] & 1
+        step_no[0] += 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(consumed[k])
+            x_bufs[k].copy_(xl, non_blocking=True)
+            arrived[k].record(s_in)
+        main.wait_event(arrived[k])
+        main.wait_event(drained[k])
+        y = managed(x_bufs[k], cuts_local)
+        o_bufs[k].copy_(y)
+        consumed[k].record(main)
+        ready[k].record(main)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ready[k])
+            ol.copy_(o_bufs[k], non_blocking=True)
+            drained[k].record(s_out)
 
-        h2d = d2h = ROWS * H * 2          # whole job: each of the N ranks moves 1/N of it
-        e2e_note = ("each rank copies its 1/N of the rows in, all-gather over NVLink, MLP, reduce-scatter, copies its "
-                    "1/N of the result out; bytes are the whole job's")
+    def e2e_join():
+        main.wait_stream(s_out)
+
+    h2d = d2h = ROWS * H * 2          # whole job: each of the N ranks moves 1/N of it
+    e2e_note = ("through DynaFlowManager.get_callable(): NanoFlow policy, 2 nano-batches, MLP subgraph substituted by the "
+                "fused kernel" + ("" if world == 1 else ", all-gather / reduce-scatter as network-tagged subgraphs on the "
+                                  "communication stream; each rank copies its 1/N of the rows in and out")
+                + ", whole-forward graph replay; H2D, step and D2H of consecutive steps on three streams")
     for _ in range(args.warmup):
         e2e_step()
+    e2e_join()
     sync.barrier()
     s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s2.record()
     for _ in range(args.steps):
         e2e_step()
+    e2e_join()
     e2.record()
     sync.barrier()
     e2e_ms = sync.max_ms(s2.elapsed_time(e2) / args.steps)
     ops.check_status()
-    # the end-to-end result, checked too: sampled rows of what came back to the host against the device-resident run
+    # the end-to-end result, checked too: what came back to the host against the device-resident run
+    results = []
+    layer.forward_device(x_dev, out_dev, cuts, results=results)
+    torch.cuda.synchronize()
     if world == 1:
-        layer.forward_device(x_dev, out_dev, cuts)
-        torch.cuda.synchronize()
-        e2e_equal = bool(torch.equal(out_host[::509], out_dev[::509].cpu()))
+        want_local = out_dev.cpu()
     else:
-        results = []
-        layer.forward_device(x_dev, out_dev, cuts, results=results)
-        torch.cuda.synchronize()
         want_local = torch.cat([results[i][lo:hi] for i, (lo, hi) in enumerate(sizes)]).cpu()
-        rel = ((ol.float() - want_local.float()).abs().max() / want_local.float().abs().max()).item()
-        e2e_equal = bool(sync.reduce_max([rel])[0] <= TOL)   # peer-order sum vs the in-switch sum: within tolerance
+    rel = ((ol.float() - want_local.float()).abs().max() / want_local.float().abs().max()).item()
+    e2e_equal = bool(sync.reduce_max([rel])[0] <= TOL)   # another summation order across ranks: within tolerance
+    e2e_substituted = managed.substituted_per_step
+    # the same step through the layer object (C ABI below TensorParallelGatedMLP), copies pipelined per micro-batch
+    if world == 1:
+        def abi_step():
+            layer.forward_host(x_host, out_host, cuts)
+    else:
+        def abi_step():
+            layer.forward_host_sliced(xl, ol, cuts, comm_in)
+    for _ in range(args.warmup):
+        abi_step()
+    sync.barrier()
+    s3, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s3.record()
+    for _ in range(max(5, args.steps // 4)):
+        abi_step()
+    e3.record()
+    sync.barrier()
+    abi_ms = sync.max_ms(s3.elapsed_time(e3) / max(5, args.steps // 4))
+    ops.check_status()
     if sampler is not None:
         sampler.stop()
 
@@ -839,7 +894,9 @@ def measure(args, sync, closers, rank: int, world: int, local_rank: int, dev) ->
         "config": dict(workload_config(world), **({"reduction": plan, "step": "one block of a dependent chain: MLP, "
                                                    "all-reduce, residual add, RMSNorm"} if world > 1 else {})),
         "e2e": {"value": ROWS / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "how": e2e_note, "result_checked": e2e_equal},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "how": e2e_note, "result_checked": e2e_equal,
+                "through_manager": True, "subgraphs_substituted_per_step": e2e_substituted,
+                "layer_object_c_abi": {"tokens_per_s": ROWS / (abi_ms * 1e-3), "ms_per_step": abi_ms}},
         "gpu_launches": launches,
         "parity": parity,
         "roofline": {"bound": "tensor",

@@ -113,6 +113,25 @@ def main() -> None:
         assert ((mine - ref).abs().max() / ro.float().abs().max()).item() <= 2e-2, f"rank {rank}: residual slice"
     dist.barrier()
 
+    # ---- the same layer step through DynaFlowManager.get_callable(): all-gather, MLP, reduce-scatter as subgraphs
+    from dynaflow_b200.host_step import ManagedLayerStep
+
+    comm_in = PeerComm(rank, world, max_rows=1024, hidden=H, slots=2, n_ctas=16, device=dev)
+    lo, hi = comm.slice_bounds(T)
+    x_local = torch.cat([x[lo:hi], x[T + lo:T + hi]]).to(dev)                 # this rank's rows of both nano-batches
+    want_local = torch.cat([want[lo:hi], want[T + lo:T + hi]])
+    for graph in (False, True):
+        step = ManagedLayerStep(layer, comm_in=comm_in, whole_forward_graph=graph)
+        for _ in range(2):
+            got = step(x_local, [0, hi - lo, 2 * (hi - lo)]).clone()
+            torch.cuda.synchronize()
+            ops.check_status()
+            rel = ((got.float().cpu() - want_local.float()).abs().max() / want.float().abs().max()).item()
+            assert rel <= 2e-2, f"rank {rank}: managed TP step rel err {rel} (graph={graph})"
+        dist.barrier()
+    comm_in.close()
+    dist.barrier()
+
     # ---- expert-parallel top-2 MoE layer: dispatch (all-gather) / expert / combine (reduce-scatter)
     from dynaflow_b200.moe import ExpertParallelMoE
 

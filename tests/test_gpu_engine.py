@@ -182,3 +182,28 @@ def test_whole_forward_graph_replays_the_recorded_schedule(model):
     t_eager, t_graph = avg_ms(eager), avg_ms(host)
     print(f"split forward, 2 layers, 2 nano-batches: eager dispatch {t_eager:.3f} ms, graph replay {t_graph:.3f} ms")
     assert t_graph < t_eager
+
+
+def test_layer_step_through_the_manager_matches_oracle(native_lib):
+    """The gated-MLP layer step driven through DynaFlowManager.get_callable(): policy, split into two
+    ragged nano-batches, native substitution of the MLP subgraph, merge; eagerly dispatched and as a
+    whole-forward graph; against the CPU oracle."""
+    from dynaflow_b200 import ops
+    from dynaflow_b200.host_step import ManagedLayerStep
+    from dynaflow_b200.layer import TensorParallelGatedMLP
+    from oracle import ops_oracle
+
+    H, I, rows = 256, 1024, 320
+    g = torch.Generator().manual_seed(40)
+    w = tuple((torch.randn(s, generator=g) * 0.05).bfloat16() for s in ((I, H), (I, H), (H, I)))
+    x = torch.randn(rows, H, generator=g).bfloat16()
+    want = ops_oracle.gated_mlp(x, *w)
+    layer = TensorParallelGatedMLP(H, I, max_rows=rows, micro_batches=2, weights=w)
+    for graph in (False, True):
+        step = ManagedLayerStep(layer, whole_forward_graph=graph)
+        for cuts in ([0, 128, 320], [0, 200, 320], [0, 128, 320]):
+            got = step(x.cuda(), cuts).clone()
+            torch.cuda.synchronize()
+            ops.check_status()
+            assert _rel(got.cpu(), want) <= TOL, (graph, cuts)
+            assert step.substituted_per_step == 2          # the MLP subgraph of both nano-batches
