@@ -1057,56 +1057,137 @@ def m_sweep(layer, dev, peaks) -> list[dict]:
 
 def run_moe(args, sync, closers, rank: int, world: int, dev) -> dict:
     """Other workload (not the default line): Mixtral-shaped top-2 MoE stack, 16384 tokens per step, 8 experts of
-    intermediate 14336, expert parallel over the launched ranks (one rank: all experts local).
-    value = tokens/s through `--moe-layers` layers (dispatch / expert / combine each)."""
+    intermediate 14336, expert parallel over the launched ranks (one rank: all experts local), two nano-batches per
+    rank in the dual-batch-overlap order (dispatch / combine of one nano-batch on the communication stream under the
+    expert GEMMs of the other, ``examples/ae/scheduler/vllm/dbo.py:168-220``). ``--moe-exchange a2a`` moves only the
+    routed rows (puts and pulls over peer memory), ``agrs`` is the all-gather / reduce-scatter form.
+    value = tokens/s through `--moe-layers` layers."""
     import torch
 
     from dynaflow_b200 import ops
     from dynaflow_b200.moe import ExpertParallelMoE
+    from oracle import ops_oracle
 
     experts, tokens, layers = 8, ROWS, args.moe_layers
     per_rank = tokens // world
+    nb_tokens = per_rank // MICRO_BATCHES                  # one nano-batch of this rank
     gen = torch.Generator(device=dev).manual_seed(7)      # same weights on every rank; each keeps its experts
 
     def weight(*shape):
         return (torch.randn(*shape, device=dev, generator=gen) * 0.02).bfloat16()
 
     stack = []
-    for _ in range(layers):
+    first_weights = None
+    for li in range(layers):
         w = (weight(experts, I, H), weight(experts, I, H), weight(experts, H, I))
-        moe = ExpertParallelMoE(H, I, experts, per_rank, rank=rank, world=world, weights=w, slots=1,
-                                n_ctas=args.comm_ctas or 32, device=dev)
+        if li == 0:
+            first_weights = tuple(t[:, :, :].clone() for t in w)
+        moe = ExpertParallelMoE(H, I, experts, nb_tokens, rank=rank, world=world, weights=w, slots=MICRO_BATCHES,
+                                n_ctas=args.comm_ctas or 32, device=dev, exchange=args.moe_exchange)
         closers.append(moe.close)
         stack.append(moe)
         del w
-    x = torch.randn(per_rank, H, device=dev, generator=gen).bfloat16()
-    logits = [torch.randn(per_rank, experts, device=dev, generator=gen).bfloat16() for _ in range(layers)]
+    x = torch.randn(per_rank, H, device=dev, generator=torch.Generator(device=dev).manual_seed(100 + rank)).bfloat16()
+    logits = [torch.randn(per_rank, experts, device=dev, generator=torch.Generator(device=dev).manual_seed(200 + 10 * li + rank)).bfloat16()
+              for li in range(layers)]
+    main = torch.cuda.current_stream(dev)
+    comm_stream = torch.cuda.Stream(device=dev)
+    outs = [[None] * MICRO_BATCHES for _ in range(layers)]
 
-    def step():
-        for layer, lg in zip(stack, logits):      # every layer routes the same rows with its own router logits
-            layer.forward(x, lg)
+    def do_expert(layer, b, gathered, x_b, lg_b):
+        if layer.exchange == "a2a":
+            return layer.expert(None, None, slot=b)          # whatever rows the last dispatch delivered
+        if gathered is None:                                  # compute only: the rows of the last full step
+            gathered = ((layer.comm_x.result(b, layer.total_tokens), layer.comm_logits.result(b, layer.total_tokens))
+                        if world > 1 else (x_b, lg_b))
+        return layer.expert(*gathered, slot=b)
 
-    for _ in range(max(3, args.warmup)):
-        step()
-    sync.barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = max(3, args.steps // 10)
-    a.record()
-    for _ in range(reps):
-        step()
-    b.record()
-    sync.barrier()
-    ms = sync.max_ms(a.elapsed_time(b) / reps)
+    def do_combine(layer, b, contrib):
+        if layer.exchange == "a2a":
+            return layer.combine(None, slot=b)
+        if contrib is None:                                   # communication only: stale contributions
+            contrib = layer.comm_out.partial(b, layer.total_tokens) if world > 1 else layer.local_contrib[b]
+        return layer.combine(contrib, slot=b)
+
+    def step(overlap: bool = True, skip_expert: bool = False, skip_comm: bool = False):
+        """Per layer: disp0 | exp0 + disp1 | exp1 + comb0 | comb1, collectives on the communication stream."""
+        cs = comm_stream if overlap else main
+        for li, (layer, lg) in enumerate(zip(stack, logits)):
+            xs = [x[b * nb_tokens:(b + 1) * nb_tokens] for b in range(MICRO_BATCHES)]
+            lgs = [lg[b * nb_tokens:(b + 1) * nb_tokens] for b in range(MICRO_BATCHES)]
+            disp, expd = [None] * MICRO_BATCHES, [None] * MICRO_BATCHES
+            gathered = [None] * MICRO_BATCHES
+            fork = torch.cuda.Event()
+            fork.record(main)
+            cs.wait_event(fork)
+            for b in range(MICRO_BATCHES):
+                with torch.cuda.stream(cs):
+                    if not skip_comm:
+                        gathered[b] = layer.dispatch(xs[b], lgs[b], slot=b)
+                    disp[b] = torch.cuda.Event()
+                    disp[b].record(cs)
+            contrib = [None] * MICRO_BATCHES
+            for b in range(MICRO_BATCHES):
+                main.wait_event(disp[b])
+                if not skip_expert:
+                    contrib[b] = do_expert(layer, b, gathered[b], xs[b], lgs[b])
+                expd[b] = torch.cuda.Event()
+                expd[b].record(main)
+                cs.wait_event(expd[b])
+                with torch.cuda.stream(cs):
+                    if not skip_comm:
+                        outs[li][b] = do_combine(layer, b, contrib[b])
+            main.wait_stream(cs)
+
+    def timed(**kw):
+        for _ in range(3):
+            step(**kw)
+        sync.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = max(3, args.steps // 10)
+        a.record()
+        for _ in range(reps):
+            step(**kw)
+        b.record()
+        sync.barrier()
+        return sync.max_ms(a.elapsed_time(b) / reps), reps
+
+    # ---- result check before timing: this rank's rows of layer 0 against the CPU oracle (sampled tokens)
+    step()
+    torch.cuda.synchronize()
+    ops.check_status()
+    got = torch.cat([outs[0][b] for b in range(MICRO_BATCHES)])
+    pick = torch.arange(0, per_rank, max(1, per_rank // 16))[:16]
+    worst = 0.0
+    host_threads()
+    wg, wu, wd = (t.cpu() for t in first_weights)
+    want = ops_oracle.moe_layer(x[pick].cpu(), logits[0][pick].cpu(), wg, wu, wd)
+    worst = ((got[pick].float().cpu() - want.float()).abs().max() / want.float().abs().max()).item()
+    worst = sync.reduce_max([worst])[0]
+    if worst > TOL:
+        raise AssertionError(f"MoE result check failed: max rel err {worst}")
+    del first_weights, wg, wu, wd
+
+    ms, reps = timed()
     ops.check_status()
     peaks, kind = measured_peaks()
     flops = 2.0 * tokens * 6.0 * H * I * layers               # two experts per token
-    line = {"workload": f"Mixtral-shaped top-2 MoE, {layers} layers, {experts} experts x {I}, {tokens} tokens per step, ep{world}",
+    line = {"workload": f"Mixtral-shaped top-2 MoE, {layers} layers, {experts} experts x {I}, {tokens} tokens per step, ep{world}, "
+                        f"{MICRO_BATCHES} nano-batches per rank in dual-batch-overlap order, exchange {args.moe_exchange}",
             "metric": "tokens/sec", "unit": "tokens/s", "n_gpus": world, "ms_per_step": ms, "value": tokens / (ms * 1e-3),
             "flops_per_step": flops, "tflops_per_gpu": flops / world / (ms * 1e-3) / 1e12,
             "frac_of_tensor_peak": flops / world / (ms * 1e-3) / 1e12 / float(peaks["bf16_tflops"]),
-            "peak_source": f"{kind} cuBLAS bf16 burst", "steps": reps, "data": "synthetic"}
-    # load balance of the first layer's routing (ids of all tokens, two experts each)
-    counts = torch.bincount(stack[0].ids[0].flatten().to(torch.int64), minlength=experts).double()
+            "peak_source": f"{kind} cuBLAS bf16 burst", "steps": reps, "data": "synthetic",
+            "parity": {"checked": True, "max_rel_err": worst, "against": "CPU oracle (ops_oracle.moe_layer), 16 sampled tokens per rank, layer 0"}}
+    if world > 1:
+        t_compute, _ = timed(skip_comm=True)
+        t_comm, _ = timed(skip_expert=True)
+        line.update({"ms_compute_only": t_compute, "ms_comm_only": t_comm,
+                     "hidden_frac": 1.0 - (ms - t_compute) / t_comm})
+        ops.check_status()
+    # load balance of the first layer's routing (ids of this rank's view, two experts each)
+    ids0 = stack[0].l_ids[0] if args.moe_exchange == "a2a" else stack[0].ids[0]
+    counts = torch.bincount(ids0.flatten().to(torch.int64), minlength=experts).double()
     line["tokens_per_expert_max_over_mean"] = float((counts.max() / counts.mean()).item())
     return line
 
@@ -1132,6 +1213,8 @@ def main() -> None:
     ap.add_argument("--replicated-residual", action="store_true",
                     help="N > 1 chain: keep the residual stream replicated on every rank instead of sharded by rows")
     ap.add_argument("--moe-layers", type=int, default=4, help="moe workload: number of layers")
+    ap.add_argument("--moe-exchange", choices=["a2a", "agrs"], default="a2a",
+                    help="moe workload: all-to-all puts / pulls of the routed rows, or all-gather / reduce-scatter of all rows")
     ap.add_argument("--decode-batch", type=int, default=256, help="decode: sequences per step")
     ap.add_argument("--kv-len", type=int, default=4096, help="decode: cached positions per sequence")
     ap.add_argument("--workload", choices=["mlp", "decoder", "decode", "moe"], default="mlp",

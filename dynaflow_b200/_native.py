@@ -31,6 +31,10 @@ class df_comm_rank_t(ctypes.Structure):
                 ("residual_in", ctypes.c_void_p), ("residual_out", ctypes.c_void_p), ("out", ctypes.c_void_p)]
 
 
+class df_a2a_rank_t(ctypes.Structure):
+    _fields_ = [("rank", ctypes.c_int), ("regions", ctypes.c_void_p * MAX_WORLD)]
+
+
 _handle = ctypes.c_ubyte * 64
 _f = ctypes.c_float
 _rank_p = ctypes.POINTER(df_comm_rank_t)
@@ -66,6 +70,16 @@ SIGNATURES: dict[str, tuple] = {
     "df_moe_gather_rows": (_i, [_vp, _vp, _vp, _i, _i, _vp, _vp]),
     "df_moe_scatter_rows": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp]),
     "df_mlp_gated_bf16_rows_on_device": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _vp, _vp]),
+    "df_a2a_region_bytes": (_sz, [_i, _i, _i, _i]),
+    "df_a2a_packed_in_offset": (_sz, [_i, _i, _i, _i]),
+    "df_a2a_packed_out_offset": (_sz, [_i, _i, _i, _i]),
+    "df_a2a_rows_total_offset": (_sz, []),
+    "df_a2a_plan": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
+    "df_a2a_dispatch_bf16": (_i, [ctypes.POINTER(df_a2a_rank_t), _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _vp, _vp]),
+    "df_a2a_combine_bf16": (_i, [ctypes.POINTER(df_a2a_rank_t), _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _vp]),
+    "df_a2a_emulated_bf16": (_i, [ctypes.POINTER(df_a2a_rank_t), _i, _i, _i, _i, _i, ctypes.POINTER(_vp), ctypes.POINTER(_vp),
+                                  ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_vp), ctypes.POINTER(_vp), _i, _i,
+                                  _vp, _vp]),
     "df_rope_bf16": (_i, [_vp, _vp, _i, _i, _i, _i, _f, _vp]),
     "df_allreduce_add_rmsnorm_bf16": (_i, [_rank_p, _i, _i, _i, _i, _vp, _f, _i, _vp, _vp]),
     "df_allreduce_add_rmsnorm_sharded_bf16": (_i, [_rank_p, _i, _i, _i, _i, _vp, _f, _i, _vp, _vp]),

@@ -298,6 +298,48 @@ int df_mlp_gated_bf16_rows_on_device(const void* x, const void* w_gate, const vo
                                      void* workspace, int capacity_rows, const int* rows_dev, int H, int I, int max_ctas,
                                      df_status_t* dev_status, void* stream);
 
+/* Expert-parallel all-to-all over peer memory: the dispatch and combine collectives of the reference's
+ * all2all managers (examples/ae/patch/vllm.patch:145-191), built as the scope asks: a peer st.global PUT
+ * kernel after an exchange of per-(source, expert) counts, and a PULL for the way back. Experts are
+ * owned in contiguous blocks (expert e lives on rank e / (experts / world)).
+ *
+ * Every rank owns one region (df_a2a_region_bytes; allocate and map it with df_comm_region_alloc /
+ * _open like the reduction regions) holding flags, the exchanged counts, per local expert the number
+ * of rows that arrived (an int at df_a2a_rows_total_offset() + 4 * local_expert: pass its address as
+ * rows_dev of df_mlp_gated_bf16_rows_on_device) and two packed buffers [local expert][capacity][hidden]
+ * at df_a2a_packed_in_offset / df_a2a_packed_out_offset: the expert MLP of local expert l reads
+ * packed_in[l] and writes packed_out[l]. capacity = total tokens of all ranks never overflows; rows
+ * beyond it would be dropped (their weight counts as zero in the combine).
+ *   df_a2a_plan      local: pos[t,c] = rank of (token t, choice c) among this rank's pairs with the
+ *                    same expert, in token order; counts[e] = pairs per expert. ids int32 [tokens, 2].
+ *   df_a2a_dispatch  counts to everyone, block-to-block barrier, every routed row of x [tokens, hidden]
+ *                    written to its place in the owner's packed_in, barrier.
+ *   df_a2a_combine   barrier (all expert outputs complete), out[t] = bf16(w[t,0] y0 + w[t,1] y1) with the
+ *                    two rows pulled from the owners' packed_out, barrier.
+ * Every rank must issue the same sequence of dispatch / combine calls on a region with the same n_ctas
+ * (<= DF_COMM_MAX_CTAS; <= 0 means 32). df_a2a_emulated_bf16 runs all ranks of one call as one
+ * cooperative launch on one GPU (test vehicle, arrays indexed by rank; combine = 0 / 1). */
+#define DF_A2A_MAX_EXPERTS 64
+typedef struct df_a2a_rank {
+  int rank;
+  void* regions[DF_COMM_MAX_WORLD];
+} df_a2a_rank_t;
+size_t df_a2a_region_bytes(int world, int experts, int capacity, int hidden);
+size_t df_a2a_packed_in_offset(int world, int experts, int capacity, int hidden);
+size_t df_a2a_packed_out_offset(int world, int experts, int capacity, int hidden);
+size_t df_a2a_rows_total_offset(void);
+int df_a2a_plan(const int* ids, int tokens, int experts, int* pos, int* counts, void* stream);
+int df_a2a_dispatch_bf16(const df_a2a_rank_t* view, int world, int experts, int capacity, int hidden, const void* x,
+                         const int* ids, const int* pos, const int* counts, int tokens, int n_ctas,
+                         df_status_t* dev_status, void* stream);
+int df_a2a_combine_bf16(const df_a2a_rank_t* view, int world, int experts, int capacity, int hidden, const int* ids,
+                        const int* pos, const float* weights, int tokens, void* out, int n_ctas,
+                        df_status_t* dev_status, void* stream);
+int df_a2a_emulated_bf16(const df_a2a_rank_t* views, int world, int experts, int capacity, int hidden, int tokens,
+                         const void* const* x, const int* const* ids, const int* const* pos, const int* const* counts,
+                         const float* const* weights, void* const* out, int combine, int n_ctas,
+                         df_status_t* dev_status, void* stream);
+
 /* Rotary position embedding (rotate-half), in place on the first `heads` heads of every row of a
  * fused qkv activation (q heads followed by k heads: pass heads = q_heads + kv_heads); row t is
  * rotated by positions[t]. Part of the attention subgraph's prologue in a decoder layer. */

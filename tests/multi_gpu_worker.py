@@ -155,6 +155,17 @@ def main() -> None:
         assert rel <= 2e-2, f"rank {rank}: expert-parallel MoE rel err {rel}"
         dist.barrier()
         moe.close()
+        # the same layer with the all-to-all exchange: only the routed rows cross the links
+        moe = ExpertParallelMoE(Hm, Im, E, per_rank, rank=rank, world=world, weights=(mg, mu, md), slots=1, n_ctas=8,
+                                device=dev, exchange="a2a")
+        for _ in range(2):
+            mine = moe.forward(xg[lo:lo + per_rank].to(dev), lg[lo:lo + per_rank].to(dev)).clone()
+        torch.cuda.synchronize()
+        ops.check_status()
+        rel = ((mine.float().cpu() - want_all[lo:lo + per_rank].float()).abs().max() / want_all.float().abs().max()).item()
+        assert rel <= 2e-2, f"rank {rank}: all-to-all MoE rel err {rel}"
+        dist.barrier()
+        moe.close()
     dist.barrier()
 
     # ---- tensor-parallel decoder stack (attention + MLP halves, reductions overlapped) vs PyTorch

@@ -194,3 +194,108 @@ def test_emulated_all_gather_and_reduce_scatter(lib, world, T, H):
         keep = torch.ones(T, dtype=torch.bool)
         keep[lo:hi] = False
         assert got[keep].abs().sum() == 0                                   # nothing written outside the own slice
+
+
+# ------------------------------------------------------------------ all-to-all form
+def test_a2a_plan_positions_and_counts(lib):
+    g = torch.Generator().manual_seed(50)
+    T, E = 1000, 8
+    ids = torch.stack([torch.randperm(E, generator=g)[:2] for _ in range(T)]).int()
+    dev = ids.cuda()
+    pos = torch.empty(T, 2, dtype=torch.int32, device="cuda")
+    counts = torch.zeros(E, dtype=torch.int32, device="cuda")
+    assert lib.df_a2a_plan(dev.data_ptr(), T, E, pos.data_ptr(), counts.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    flat = ids.flatten()
+    want_pos = torch.empty_like(flat)
+    seen = [0] * E
+    for i, e in enumerate(flat.tolist()):
+        want_pos[i] = seen[e]
+        seen[e] += 1
+    assert torch.equal(pos.cpu().flatten(), want_pos) and counts.cpu().tolist() == seen
+
+
+@pytest.mark.parametrize("world,Tr,H,E", [(2, 64, 256, 8), (8, 100, 512, 8), (4, 37, 64, 16)])
+def test_emulated_a2a_dispatch_and_combine(lib, world, Tr, H, E):
+    """All ranks of the all-to-all as one cooperative launch on one GPU: every routed row lands in the
+    owner's packed input grouped by source rank in token order (bit-exact), the arrived-row counts are
+    right, and the combine pulls each token's two expert rows back with its routing weights."""
+    import ctypes
+
+    from dynaflow_b200 import ops
+    from dynaflow_b200._native import df_a2a_rank_t
+    from oracle import ops_oracle
+
+    g = torch.Generator().manual_seed(51 + world)
+    cap, per = Tr * world, E // world
+    xs = [torch.randn(Tr, H, generator=g).bfloat16() for _ in range(world)]
+    routed = [ops_oracle.top2_route(torch.randn(Tr, E, generator=g).bfloat16()) for _ in range(world)]
+    nbytes = lib.df_a2a_region_bytes(world, E, cap, H)
+    in_off, out_off = lib.df_a2a_packed_in_offset(world, E, cap, H), lib.df_a2a_packed_out_offset(world, E, cap, H)
+    rows_off = lib.df_a2a_rows_total_offset()
+    regions = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    views = (df_a2a_rank_t * world)()
+    for r in range(world):
+        views[r].rank = r
+        for q in range(world):
+            views[r].regions[q] = regions[q].data_ptr()
+    x_dev = [x.cuda() for x in xs]
+    ids_dev = [ids.int().cuda() for _w, ids in routed]
+    w_dev = [w.float().cuda() for w, _ids in routed]
+    pos_dev = [torch.empty(Tr, 2, dtype=torch.int32, device="cuda") for _ in range(world)]
+    cnt_dev = [torch.zeros(E, dtype=torch.int32, device="cuda") for _ in range(world)]
+    out_dev = [torch.zeros(Tr, H, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    for r in range(world):
+        assert lib.df_a2a_plan(ids_dev[r].data_ptr(), Tr, E, pos_dev[r].data_ptr(), cnt_dev[r].data_ptr(), None) == 0
+
+    def ptrs(ts):
+        return (ctypes.c_void_p * world)(*[t.data_ptr() for t in ts])
+
+    st = ops.status_block()
+    for call in range(2):                                            # the flags carry a sequence number: twice
+        rc = lib.df_a2a_emulated_bf16(views, world, E, cap, H, Tr, ptrs(x_dev), ptrs(ids_dev), ptrs(pos_dev), ptrs(cnt_dev),
+                                      None, None, 0, 4, st.data_ptr(), None)
+        assert rc == 0
+        torch.cuda.synchronize()
+        ops.check_status()
+        for e in range(E):
+            d, el = e // per, e % per
+            want_rows = torch.cat([xs[s][(routed[s][1] == e).any(dim=1)] for s in range(world)])
+            n = want_rows.shape[0]
+            total = regions[d][rows_off + 4 * el: rows_off + 4 * el + 4].view(torch.int32).item()
+            assert total == n, (e, total, n)
+            got = regions[d][in_off + el * cap * H * 2: in_off + (el * cap + n) * H * 2].view(torch.bfloat16).view(n, H)
+            assert torch.equal(got.cpu(), want_rows), e
+            # stand-in for the expert: its output rows are the input rows scaled by (e + 1) / 8
+            out_rows = regions[d][out_off + el * cap * H * 2: out_off + (el * cap + n) * H * 2].view(torch.bfloat16).view(n, H)
+            out_rows.copy_((got.float() * ((e + 1) / 8)).bfloat16())
+        rc = lib.df_a2a_emulated_bf16(views, world, E, cap, H, Tr, None, ptrs(ids_dev), ptrs(pos_dev), None, ptrs(w_dev),
+                                      ptrs(out_dev), 1, 4, st.data_ptr(), None)
+        assert rc == 0
+        torch.cuda.synchronize()
+        ops.check_status()
+        for r in range(world):
+            w, ids = routed[r]
+            y = [(xs[r].float() * ((ids[:, c].float() + 1) / 8).unsqueeze(1)).bfloat16().float() for c in range(2)]
+            want = (y[0] * w[:, 0:1] + y[1] * w[:, 1:2]).bfloat16()
+            assert _rel(out_dev[r], want) <= 1e-2, (call, r)
+
+
+@pytest.mark.parametrize("T,H,I,E", [(300, 256, 512, 8), (64, 128, 256, 16)])
+def test_single_rank_moe_layer_all_to_all_form(lib, T, H, I, E):
+    from dynaflow_b200 import ops
+    from dynaflow_b200.moe import ExpertParallelMoE
+    from oracle import ops_oracle
+
+    g = torch.Generator().manual_seed(52)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    logits = torch.randn(T, E, generator=g).bfloat16()
+    w = tuple((torch.randn(*s, generator=g) * 0.05).bfloat16() for s in ((E, I, H), (E, I, H), (E, H, I)))
+    layer = ExpertParallelMoE(H, I, E, T, weights=w, slots=1, exchange="a2a", n_ctas=8)
+    got = layer.forward(x.cuda(), logits.cuda()).clone()
+    again = layer.forward(x.cuda(), logits.cuda())
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(got, again)
+    assert _rel(got, ops_oracle.moe_layer(x, logits, *w)) <= TOL
+    layer.close()
