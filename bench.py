@@ -391,7 +391,8 @@ class RankSync:
     def barrier(self) -> None:
         import torch
 
-        torch.cuda.synchronize()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
         self.reduce_max([0.0])
 
     def max_ms(self, ms: float) -> float:
@@ -400,6 +401,34 @@ class RankSync:
     def all_equal(self, digest: float) -> bool:
         hi, neg_lo = self.reduce_max([digest, -digest])
         return hi == -neg_lo
+
+
+def leave_together(sync: RankSync, closers: list, error: str | None, learned: bool) -> str | None:
+    """Every rank leaves together, whatever happened: tell the others (unless this rank learned of a
+    failure at a synchronisation point, which consumed that exchange), stop launching, meet, unmap the
+    communicators, meet again. Returns the error to exit with (its own, or that a peer failed)."""
+    import torch
+
+    if sync.world > 1:
+        if not learned:
+            try:
+                sync.reduce_max([0.0], fail=error is not None)
+            except PeerFailed as exc:
+                error = error or str(exc)
+        if torch.cuda.is_available():
+            try:
+                torch.cuda.synchronize()
+            except Exception:  # noqa: BLE001
+                traceback.print_exc()
+        sync.reduce_max([0.0], quiet=True)
+    for close in reversed(closers):
+        try:
+            close()
+        except Exception:  # noqa: BLE001
+            traceback.print_exc()
+    if sync.world > 1:
+        sync.reduce_max([0.0], quiet=True)
+    return error
 
 
 def digest_of(t) -> float:
@@ -954,25 +983,8 @@ def run_ours(args) -> None:
     except Exception as exc:  # noqa: BLE001 -- reported after every rank has left together
         traceback.print_exc()
         error = f"{type(exc).__name__}: {exc}"
-    # ---- every rank leaves together, whatever happened: tell the others, stop launching, unmap, exit
+    error = leave_together(sync, closers, error, learned)
     if world > 1:
-        if not learned:
-            try:
-                sync.reduce_max([0.0], fail=error is not None)
-            except PeerFailed as exc:
-                error = error or str(exc)
-        try:
-            torch.cuda.synchronize()
-        except Exception:  # noqa: BLE001
-            traceback.print_exc()
-        sync.reduce_max([0.0], quiet=True)
-    for close in reversed(closers):
-        try:
-            close()
-        except Exception:  # noqa: BLE001
-            traceback.print_exc()
-    if world > 1:
-        sync.reduce_max([0.0], quiet=True)
         dist.destroy_process_group()
     if error is not None:
         print(f"[bench] rank {rank} failed: {error}", file=sys.stderr)

@@ -69,3 +69,65 @@ def test_two_gloo_ranks(tmp_path):
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
     assert proc.returncode == 0, (proc.stdout[-2000:], proc.stderr[-3000:])
     assert "CPU_MULTIRANK_OK" in proc.stdout
+
+
+EXIT_WORKER = textwrap.dedent("""
+    import os, sys, time
+    import torch, torch.distributed as dist
+    sys.path.insert(0, {root!r})
+    import bench
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    mode = sys.argv[1]
+    dist.init_process_group("gloo")
+    sync = bench.RankSync(world, torch.device("cpu"))
+    log = []
+    closers = [lambda: log.append(("closed", time.time()))]
+    error, learned = None, False
+    try:
+        assert sync.max_ms(1.0 + rank) == float(world)            # ordinary use: the maximum over ranks
+        assert sync.all_equal(7.0) and not sync.all_equal(float(rank))
+        if mode == "fail" and rank == 1:
+            raise RuntimeError("rank 1 breaks here")                # the others are on their way to the next meeting point
+        time.sleep(0.2 * rank)
+        sync.barrier()
+        sync.barrier()
+    except bench.PeerFailed as exc:
+        error, learned = str(exc), True
+    except Exception as exc:
+        error = str(exc)
+    error = bench.leave_together(sync, closers, error, learned)
+    assert len(log) == 1                                             # every rank unmapped exactly once
+    # nobody unmapped before everybody had stopped: the closers ran after the second meeting point on all ranks
+    stamps = [None] * world
+    dist.all_gather_object(stamps, (log[0][1], error))
+    dist.destroy_process_group()
+    if mode == "fail":
+        assert all(e is not None for _t, e in stamps), stamps        # the failure reached every rank
+        assert (error == "rank 1 breaks here") == (rank == 1)
+        print(f"RANK{{rank}}_LEFT_WITH_ERROR")
+        sys.exit(1)
+    assert all(e is None for _t, e in stamps), stamps
+    print(f"RANK{{rank}}_LEFT_CLEAN")
+""")
+
+
+def _run_exit_worker(tmp_path, mode, port):
+    script = tmp_path / f"exit_{mode}.py"
+    script.write_text(EXIT_WORKER.format(root=ROOT))
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), str(script), mode]
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
+
+
+def test_ranks_leave_together_clean_and_after_a_failure(tmp_path):
+    """bench.py's exit protocol on three gloo ranks: every host-side collective has one shape, so a rank
+    that fails still pairs with the synchronisation its peers reach next; they learn of it there, and all
+    ranks run their closers between the same two meeting points and exit non-zero."""
+    ok = _run_exit_worker(tmp_path, "clean", 29741)
+    assert ok.returncode == 0, (ok.stdout[-2000:], ok.stderr[-3000:])
+    assert all(f"RANK{r}_LEFT_CLEAN" in ok.stdout for r in range(3))
+    bad = _run_exit_worker(tmp_path, "fail", 29742)
+    assert bad.returncode != 0
+    assert all(f"RANK{r}_LEFT_WITH_ERROR" in bad.stdout for r in range(3)), (bad.stdout[-2000:], bad.stderr[-3000:])
