@@ -54,16 +54,25 @@ constexpr int BKV = 128;  // keys per block
 constexpr int HD = 128;   // head dimension (the only one built)
 constexpr int TILE_BYTES = 128 * 128 * 2;
 constexpr int HALF_BYTES = TILE_BYTES / 2;  // one TMA box: 128 rows x 64 columns
-constexpr int KV_SLOTS = 5;   // ring of key and value tiles: K_0 V_0 K_1 V_1 ... in this order
+// Ring of key and value tiles, K_0 V_0 K_1 V_1 ... in this order. Prefill: two 32 KB query tiles and five
+// slots. Decode: the few query-head rows take 1 KB per 64-column half (the MMA still addresses 128 rows per
+// half; the rows beyond the heads alias the ring and are never read back), which leaves room for seven slots:
+// the launch is bound by the bytes in flight from HBM.
+constexpr int KV_SLOTS_PREFILL = 5;
+constexpr int KV_SLOTS_DECODE = 7;
+constexpr int KV_SLOTS_MAX = 7;
+constexpr int DECODE_Q_BYTES = 2048;      // two halves of 8 rows x 128 B
+constexpr int DECODE_MAX_GROUP = 8;       // query heads per key/value head that fit those rows
 constexpr int THREADS = 384;  // warps 0..2 producer / MMA / tensor-memory owner, 3 idle, 4..11 softmax
 constexpr int TMEM_COLS = 512;  // S (and P) of tile 0, of tile 1, O of tile 0, O of tile 1: 4 x 128 columns
 constexpr int O_COL = 256;
 constexpr int kBarrierBytes = 256;
 // two Q tiles, the ring, barriers; what is left of the 227 KB is the room the 1024-byte alignment
 // of the tiles may cost (checked in the kernel)
-constexpr int kSmemUsed = (2 + KV_SLOTS) * TILE_BYTES + kBarrierBytes;
+constexpr int kSmemUsedPrefill = (2 + KV_SLOTS_PREFILL) * TILE_BYTES + kBarrierBytes;
+constexpr int kSmemUsedDecode = DECODE_Q_BYTES + KV_SLOTS_DECODE * TILE_BYTES + kBarrierBytes;
 constexpr int SMEM_BYTES = 227 * 1024;
-static_assert(kSmemUsed <= SMEM_BYTES, "shared-memory budget");
+static_assert(kSmemUsedPrefill <= SMEM_BYTES && kSmemUsedDecode <= SMEM_BYTES, "shared-memory budget");
 constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units
 
 enum : unsigned {
@@ -198,14 +207,17 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
   uint8_t* smem = smem_raw + pad;
-  uint8_t* sQ = smem;                    // two tiles
-  uint8_t* sKV = sQ + 2 * TILE_BYTES;    // KV_SLOTS tiles
+  constexpr int KV_SLOTS = DECODE ? KV_SLOTS_DECODE : KV_SLOTS_PREFILL;
+  constexpr int Q_HALF_STRIDE = DECODE ? DECODE_Q_BYTES / 2 : HALF_BYTES;  // distance of the two 64-column halves of Q
+  constexpr int kSmemUsed = DECODE ? kSmemUsedDecode : kSmemUsedPrefill;
+  uint8_t* sQ = smem;                                                   // prefill: two tiles; decode: the head rows
+  uint8_t* sKV = sQ + (DECODE ? DECODE_Q_BYTES : 2 * TILE_BYTES);       // KV_SLOTS tiles
   uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + KV_SLOTS * TILE_BYTES);
   uint64_t* q_full = bars;
   uint64_t* q_empty = bars + 1;
   uint64_t* kv_full = bars + 2;
-  uint64_t* kv_empty = kv_full + KV_SLOTS;
-  uint64_t* s_full = kv_empty + KV_SLOTS;
+  uint64_t* kv_empty = kv_full + KV_SLOTS_MAX;
+  uint64_t* s_full = kv_empty + KV_SLOTS_MAX;
   uint64_t* p_full = s_full + 2;
   uint64_t* pv_done = p_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
@@ -269,7 +281,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           // the group's query heads of this sequence: rows 0..group-1 of tile 0
           mbar_expect_tx(q_full, 2 * p.group * 128);
           tma_load_3d(sQ, &tm_q, q_full, 0, w.head, w.q_row);
-          tma_load_3d(sQ + HALF_BYTES, &tm_q, q_full, 64, w.head, w.q_row);
+          tma_load_3d(sQ + Q_HALF_STRIDE, &tm_q, q_full, 64, w.head, w.q_row);
         } else {
           const int tiles = w.nb[1] > 0 ? 2 : 1;
           mbar_expect_tx(q_full, tiles * TILE_BYTES);
@@ -331,7 +343,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const uint32_t k_addr = kv_addr + slot * TILE_BYTES;
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
-          const uint64_t da = make_desc_k_sw128(q_addr + G * TILE_BYTES + (k >> 2) * HALF_BYTES) + 2u * (k & 3);
+          const uint64_t da = make_desc_k_sw128(q_addr + G * TILE_BYTES + (k >> 2) * Q_HALF_STRIDE) + 2u * (k & 3);
           const uint64_t db = make_desc_k_sw128(k_addr + (k >> 2) * HALF_BYTES) + 2u * (k & 3);
           umma_bf16(d, da, db, idesc_qk, k > 0 ? 1u : 0u);
         }
@@ -771,7 +783,8 @@ extern "C" int df_attention_decode_bf16(const void* q, const void* k_cache, cons
   if (batch <= 0 || max_len <= 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0)
     return fail(DF_EINVAL, "batch, max_len and the head counts must be positive, q_heads a multiple of kv_heads");
   const int group = q_heads / kv_heads;
-  if (group > 32) return fail(DF_EUNSUPPORTED, "at most 32 query heads per key/value head (got %d)", group);
+  if (group > DECODE_MAX_GROUP)
+    return fail(DF_EUNSUPPORTED, "at most %d query heads per key/value head (got %d)", DECODE_MAX_GROUP, group);
   if (static_cast<long long>(batch) * max_len > 0x7fffffffLL) return fail(DF_EUNSUPPORTED, "batch * max_len exceeds 2^31 rows");
   if (ld_q < q_heads * HD || ld_kv < kv_heads * HD || ld_out < q_heads * HD || (ld_q % 8) != 0 || (ld_kv % 8) != 0 ||
       (ld_out % 8) != 0)

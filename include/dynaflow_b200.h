@@ -379,7 +379,7 @@ int df_attention_prefill_bf16(const void* q, const void* k, const void* v, void*
  * The keys of a sequence are cut into chunks that different CTAs process (split-KV); `workspace`
  * (df_attention_decode_workspace_bytes, 16-byte aligned, contents arbitrary) receives the chunks'
  * partial results, which a second small launch merges. seq_lens_dev stays in device memory, so a
- * captured graph follows growing sequences. head_dim must be 128, q_heads / kv_heads <= 32. */
+ * captured graph follows growing sequences. head_dim must be 128, q_heads / kv_heads <= 8. */
 size_t df_attention_decode_workspace_bytes(int batch, int q_heads, int kv_heads, int max_len);
 int df_attention_decode_bf16(const void* q, const void* k_cache, const void* v_cache, void* out,
                              const int* seq_lens_dev, int batch, int max_len, int q_heads, int kv_heads,
