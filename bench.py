@@ -609,6 +609,11 @@ def decode_block(args, sync, closers, rank: int, world: int, dev, plan: dict) ->
     from dynaflow_b200.decoder import DecoderShape, TensorParallelDecoder
 
     shape = DecoderShape(layers=args.layers)
+    if args.shard_of > 1:
+        # one rank's share of an N-way tensor-parallel step on this GPU alone (no reductions): per-kernel profiling
+        n = args.shard_of
+        shape = DecoderShape(layers=args.layers, heads=shape.heads // n, kv_heads=shape.kv_heads // n,
+                             intermediate=shape.intermediate // n, vocab=shape.vocab // n)
     batch, kv_len = args.decode_batch, args.kv_len
     dec = TensorParallelDecoder(shape, rank=rank, world=world, max_rows=batch // MICRO_BATCHES,
                                 micro_batches=MICRO_BATCHES, seed=0, device=dev, n_ctas=max(plan["comm_ctas"], 1),
@@ -1229,6 +1234,8 @@ def main() -> None:
                     help="moe workload: all-to-all puts / pulls of the routed rows, or all-gather / reduce-scatter of all rows")
     ap.add_argument("--decode-batch", type=int, default=256, help="decode: sequences per step")
     ap.add_argument("--kv-len", type=int, default=4096, help="decode: cached positions per sequence")
+    ap.add_argument("--shard-of", type=int, default=1, help="decode on one GPU: run one rank's share of an N-way "
+                    "tensor-parallel step (heads, key/value heads, intermediate and vocabulary divided by N, no reductions)")
     ap.add_argument("--workload", choices=["mlp", "decoder", "decode", "moe"], default="mlp",
                     help="mlp: the fused gated-MLP layer step (the benchmark line, which also carries the decoder "
                          "block); decoder / moe: that workload alone")

@@ -38,6 +38,7 @@
 #include <mutex>
 
 #include "../../include/dynaflow_b200.h"
+#include "gemm_internal.h"
 #include "host_util.h"
 #include "ptx.cuh"
 
@@ -921,8 +922,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
 // ------------------------------------------------------------------- host
 
-static bool make_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
-                          uint32_t box_rows) {
+bool make_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
   PFN_encodeTiled fn = get_encode_tiled();
   if (fn == nullptr) return false;
   cuuint64_t gdim[2] = {cols, rows};
@@ -943,7 +943,7 @@ static bool make_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uin
 
 // Launch-form options (df_set_launch_option): which of the bit-different but equally valid
 // forms of a launch is chosen. Process-wide, read at every launch.
-static std::atomic<int> g_launch_option[DF_OPT_COUNT_] = {{1}, {1}, {1}};
+static std::atomic<int> g_launch_option[DF_OPT_COUNT_] = {{1}, {1}, {1}, {1}};
 static int launch_option(int opt) { return g_launch_option[opt].load(std::memory_order_relaxed); }
 
 // Development knobs exist only in builds with -DDF_DEV_KNOBS (integers taken from the
@@ -1224,7 +1224,17 @@ static int launch_gemm(const void* a, const void* b0, const void* b1, void* c, i
   int sms = df_sm_count();
   if (sms <= 0) return fail(DF_ECUDA, "no CUDA device");
 
-  // At most 128 rows: the operand-swapped form with a smaller A stage and a deeper pipeline.
+  // At most 128 rows: the split-K kernel made for launches that stream the weights once.
+  if (M <= BM && m_dev == nullptr && launch_option(DF_OPT_SPLIT_K_SMALL) != 0 && tuning_int("DF_GEMM_CTAS", 1) != 2) {
+    int units = sms;
+    if (max_ctas > 0 && max_ctas < units) units = max_ctas;
+    const int r = launch_small_rows(MODE == MODE_GATEUP, a, b0, b1, c, M, N, K, lda, ldb, ldc, units,
+                                    launch_option(DF_OPT_STREAM_K) != 0, tuning_int("DF_SMALL_BH", 0),
+                                    tuning_int("DF_SMALL_SPLITS", 0), dev_status, static_cast<cudaStream_t>(stream));
+    if (r != DF_SMALL_NOT_APPLICABLE) return r;
+  }
+
+  // Otherwise, at most 128 rows: the operand-swapped form with a smaller A stage and a deeper pipeline.
   const bool skinny = M <= tuning_int("DF_GEMM_SKINNY_ROWS", 128) && M <= BM && m_dev == nullptr && launch_option(DF_OPT_OPERAND_SWAP) != 0 &&
                       tuning_int("DF_GEMM_CTAS", 1) != 2;
   const int a_rows = skinny ? ((M + 15) / 16) * 16 : BM;

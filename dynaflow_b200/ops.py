@@ -17,7 +17,7 @@ from . import _native
 from ._native import df_status_t
 
 DEVICE_ERRORS = {1: "DF_ERR_TIMEOUT", 2: "DF_ERR_PEER"}
-_WHERE = {1: "tma-producer", 2: "mma(full)", 3: "mma(tmem-empty)", 4: "epilogue", 5: "h-ready", 16: "peer-flag", 32: "attention-producer", 33: "attention-mma", 34: "attention-softmax"}
+_WHERE = {1: "tma-producer", 2: "mma(full)", 3: "mma(tmem-empty)", 4: "epilogue", 5: "h-ready", 16: "peer-flag", 21: "small-gemm-producer", 22: "small-gemm-mma", 23: "small-gemm-epilogue", 24: "small-gemm-partial-rows", 32: "attention-producer", 33: "attention-mma", 34: "attention-softmax"}
 
 
 class DeviceStatusError(RuntimeError):
@@ -72,7 +72,7 @@ def set_timeout_ms(ms: int) -> None:
         raise ValueError(_native.last_error())
 
 
-LAUNCH_OPTIONS = {"stream_k": 0, "mlp_one_launch": 1, "operand_swap": 2}
+LAUNCH_OPTIONS = {"stream_k": 0, "mlp_one_launch": 1, "operand_swap": 2, "split_k_small": 3}
 
 
 def set_launch_option(name: str, on: bool) -> None:

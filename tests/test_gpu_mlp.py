@@ -213,12 +213,22 @@ def test_one_launch_mlp_equals_two_launches(ops, M, H, I):
     assert torch.equal(small, two)
 
 
+@pytest.fixture(params=[True, False], ids=["split_k_small", "operand_swap"])
+def small_rows_form(request, ops):
+    """Both forms a launch of at most 128 rows can take: the split-K kernel (default) and, with it
+    switched off, the operand-swapped form of the general kernel."""
+    ops.set_launch_option("split_k_small", request.param)
+    yield request.param
+    ops.set_launch_option("split_k_small", True)
+
+
 @pytest.mark.parametrize("M", [1, 7, 16, 17, 48, 64, 65, 100, 127, 128])
 @pytest.mark.parametrize("H,I", [(4096, 14336), (1024, 2816)])
-def test_decode_rows_operand_swapped_form(ops, M, H, I):
-    """Launches of at most 128 rows take the operand-swapped form of the GEMM kernel (weight rows on
-    the accumulator lanes, token rows on its columns, stream-K partial sums finished cooperatively).
-    Against the oracle, against the regular form, bit-reproducible, and nothing written past row M."""
+def test_decode_rows_operand_swapped_form(ops, M, H, I, small_rows_form):
+    """Launches of at most 128 rows take the split-K kernel or the operand-swapped form of the GEMM
+    kernel (weight rows on the accumulator lanes, token rows on its columns, stream-K partial sums
+    finished cooperatively). Against the oracle, against the regular form, bit-reproducible, and
+    nothing written past row M."""
     from oracle import ops_oracle
 
     x = _rand((M, H), 1.0, 21)
@@ -244,6 +254,35 @@ def test_decode_rows_operand_swapped_form(ops, M, H, I):
         ops.set_launch_option("operand_swap", True)
     ops.check_status()
     assert rel_err(out, regular) <= 1e-2
+
+
+@pytest.mark.parametrize("M", [1, 8, 50, 128])
+@pytest.mark.parametrize("N,K", [(768, 4096), (4096, 512), (4096, 1792), (200, 72), (16032, 4096)])
+def test_split_k_small_gemm(ops, M, N, K):
+    """The projections of a decode step (at most 128 rows): (tile, k range) CTAs that exchange fp32
+    partial tiles with bulk copies and sum them in k order. Against an fp32 product, bit-reproducible,
+    nothing written outside the output view, and in agreement with the one-CTA-per-tile form and
+    with the general kernel."""
+    a, b = _rand((M, K), 1.0, 31).cuda(), _rand((N, K), 0.03, 32).cuda()
+    canvas = torch.full((M + 2, N + 16), 7.0, dtype=torch.bfloat16, device="cuda")
+    out = canvas[:M, 8:8 + N]
+    ops.gemm_bf16(a, b, out=out)
+    first = out.clone()
+    for _ in range(3):
+        ops.gemm_bf16(a, b, out=out)
+        assert torch.equal(out, first)
+    ops.check_status()
+    assert torch.all(canvas[M:] == 7.0) and torch.all(canvas[:, :8] == 7.0) and torch.all(canvas[:, 8 + N:] == 7.0)
+    want = a.float() @ b.float().T
+    assert rel_err(out, want) <= TOL
+    for option in ("stream_k", "split_k_small"):
+        ops.set_launch_option(option, False)
+        try:
+            other = ops.gemm_bf16(a, b)
+        finally:
+            ops.set_launch_option(option, True)
+        ops.check_status()
+        assert rel_err(other, out) <= 1e-2
 
 
 @pytest.mark.parametrize("M", [2048, 8192, 16384])
