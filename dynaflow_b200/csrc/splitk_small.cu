@@ -28,6 +28,7 @@
 
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "../../include/dynaflow_b200.h"
@@ -59,7 +60,16 @@ struct SmallParams {
   __nv_bfloat16* C;
   Status* status;
   unsigned long long timeout_ns;
+#ifdef DF_DEV_KNOBS
+  unsigned long long* timing;  // development builds: eight time stamps per CTA, or NULL
+#endif
 };
+
+#ifdef DF_DEV_KNOBS
+#define SMALL_STAMP(i) do { if (p.timing != nullptr) p.timing[blockIdx.x * 8 + (i)] = globaltimer_ns(); } while (0)
+#else
+#define SMALL_STAMP(i) do { } while (0)
+#endif
 
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
@@ -116,6 +126,7 @@ splitk_small_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const int n0 = tile * (MODE == SMALL_GATEUP ? p.bh : 2 * p.bh);  // first output column of the tile
 
   if (threadIdx.x == 0) {
+    SMALL_STAMP(0);
     for (int s = 0; s < p.stages; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -138,6 +149,7 @@ splitk_small_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   // first cluster barrier, split in two: arriving here says "this CTA runs, its shared memory and
   // barriers exist"; the wait comes before the first copy into another CTA
   if (S > 1) cluster_arrive();
+  if (threadIdx.x == 0) SMALL_STAMP(1);
 
   const uint32_t tmem_base = *tmem_slot;
   const Deadline dl{globaltimer_ns() + p.timeout_ns, abort_flag, p.status};
@@ -177,6 +189,8 @@ splitk_small_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           break;
         }
         tc_fence_after();
+        if (kb == kb0) SMALL_STAMP(2);
+        if (kb == kb1 - 1) SMALL_STAMP(3);
         const uint32_t a_addr = smem_u32(smem + stage * stage_bytes);
         const uint64_t da = make_desc_k_sw128(a_addr);
         const uint64_t db = make_desc_k_sw128(a_addr + static_cast<uint32_t>(p.a_bytes));
@@ -202,6 +216,7 @@ splitk_small_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     bool ok = mbar_wait(tfull, 0u, dl, WHERE_SMALL_EPILOGUE, blockIdx.x);
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
+    if (tid == 0) SMALL_STAMP(4);
     const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
 
     if (S == 1) {
@@ -269,6 +284,7 @@ splitk_small_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const int slot_bytes = p.rows_per * row_bytes;
       const int my_r0 = s_idx * p.rows_per;
       const int my_rows = max(0, min(p.M - my_r0, p.rows_per));
+      if (tid == 0) SMALL_STAMP(5);
       if (tid == 0 && !*abort_flag) {
         if (my_rows > 0) mbar_expect_tx(recv_bar, static_cast<uint32_t>(S * my_rows * row_bytes));
         const uint32_t slot_local = smem_u32(recv) + static_cast<uint32_t>(s_idx * slot_bytes);
@@ -285,6 +301,7 @@ splitk_small_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       bool got = true;
       if (my_rows > 0) got = mbar_wait(recv_bar, 0u, dl, WHERE_SMALL_RECV, blockIdx.x);
       got = __all_sync(0xffffffffu, got);
+      if (tid == 0) SMALL_STAMP(6);
       cluster_arrive();  // second cluster barrier, waited for at the very end
       const int r0 = my_r0;
       const int nrows = my_rows;
@@ -337,6 +354,7 @@ splitk_small_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   __syncwarp();
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) SMALL_STAMP(7);
   if (warp == 2) {
     tc_fence_after();
     if (*abort_flag) {
@@ -353,10 +371,10 @@ struct Plan {
   double cost;
 };
 
-// Rough time model (microseconds) of one launch form; only the ordering of the candidates matters.
-// Per CTA: a round trip per ring refill plus its bytes at the rate one SM takes them in, or its
-// MMAs if they take longer; over the whole launch: all bytes at the rate L2 and HBM deliver
-// them; then the exchange inside the cluster.
+// Time model (microseconds, without the launch itself) of one launch form, fitted to per-CTA time
+// stamps on a B200: a CTA takes its operand bytes in at about 90 GB/s and all CTAs together at
+// about 8.5 TB/s (the rows of A are re-read from L2 by every tile); a cluster exchange costs about
+// a microsecond plus the bytes a CTA sends at the 28 GB/s one SM reaches into another's shared memory.
 static bool evaluate(int M, int N, int num_kb, bool gateup, int units, int bh, int splits, Plan* out) {
   const int out_per_tile = gateup ? bh : 2 * bh;
   const int tiles = (N + out_per_tile - 1) / out_per_tile;
@@ -382,12 +400,14 @@ static bool evaluate(int M, int N, int num_kb, bool gateup, int units, int bh, i
   if (waves > 1 && splits > 1) return false;  // more than a wave of tiles: nothing to gain from splitting
   const int rounds = (kb_per + stages - 1) / stages;
   const double cta_bytes = static_cast<double>(kb_per) * stage_bytes;
-  const double t_copy = rounds * 1.0 + cta_bytes / 120e3;
-  const double t_mma = 0.8 + kb_per * 4.0 * (bh + 28) / 1900.0;
-  const double t_cta = t_copy > t_mma ? t_copy : t_mma;
-  const double t_all = static_cast<double>(ctas) * cta_bytes / 6.0e6;
-  double t = t_cta * waves > t_all ? t_cta * waves : t_all;
-  t += splits > 1 ? 0.8 + M * row_bytes / 200e3 : M * row_bytes / 2 / 100e3;
+  const double t_one = cta_bytes / 90e3 * waves;
+  const double t_all = static_cast<double>(ctas) * cta_bytes / 8.5e6;
+  double t = (t_one > t_all ? t_one : t_all) + 1.7 + 0.3 * (rounds - 1);
+  const double tile_bytes = static_cast<double>(M) * row_bytes;
+  if (splits > 1)
+    t += 0.4 + 1.0 + tile_bytes * (splits - 1) / splits / 28e3 + 0.5;
+  else
+    t += tile_bytes / 2 / 40e3 * waves;
   out->bh = bh;
   out->splits = splits;
   out->stages = stages;
@@ -442,6 +462,10 @@ static int launch_small_mode(const void* a, const void* b0, const void* b1, void
   p.C = static_cast<__nv_bfloat16*>(c);
   p.status = reinterpret_cast<Status*>(dev_status);
   p.timeout_ns = timeout_ns();
+#ifdef DF_DEV_KNOBS
+  const char* tp = std::getenv("DF_SMALL_TIMING_PTR");
+  p.timing = tp != nullptr ? reinterpret_cast<unsigned long long*>(std::strtoull(tp, nullptr, 0)) : nullptr;
+#endif
 
   auto kernel = splitk_small_kernel<MODE>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM_CAP);
