@@ -701,6 +701,8 @@ __global__ void kv_cache_append_kernel(const __nv_bfloat16* __restrict__ k_new, 
 }  // namespace attn
 }  // namespace df
 
+#include "attention_decode.cuh"
+
 extern "C" int df_attention_prefill_bf16(const void* q, const void* k, const void* v, void* out, int total_rows, int batch,
                                          int seq_len, const int* cu_seqlens_dev, int q_heads, int kv_heads, int head_dim,
                                          int ld_q, int ld_k, int ld_v, int ld_out, float scale, int max_ctas,
@@ -783,8 +785,8 @@ extern "C" int df_attention_decode_bf16(const void* q, const void* k_cache, cons
   if (batch <= 0 || max_len <= 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0)
     return fail(DF_EINVAL, "batch, max_len and the head counts must be positive, q_heads a multiple of kv_heads");
   const int group = q_heads / kv_heads;
-  if (group > DECODE_MAX_GROUP)
-    return fail(DF_EUNSUPPORTED, "at most %d query heads per key/value head (got %d)", DECODE_MAX_GROUP, group);
+  if (group > T_MAX_GROUP)
+    return fail(DF_EUNSUPPORTED, "at most %d query heads per key/value head (got %d)", T_MAX_GROUP, group);
   if (static_cast<long long>(batch) * max_len > 0x7fffffffLL) return fail(DF_EUNSUPPORTED, "batch * max_len exceeds 2^31 rows");
   if (ld_q < q_heads * HD || ld_kv < kv_heads * HD || ld_out < q_heads * HD || (ld_q % 8) != 0 || (ld_kv % 8) != 0 ||
       (ld_out % 8) != 0)
@@ -826,18 +828,24 @@ extern "C" int df_attention_decode_bf16(const void* q, const void* k_cache, cons
   if (!make_map(&tm_k, k_cache, cache_rows, static_cast<uint64_t>(kv_heads) * HD, ld_kv)) return DF_ECUDA;
   if (!make_map(&tm_v, v_cache, cache_rows, static_cast<uint64_t>(kv_heads) * HD, ld_kv)) return DF_ECUDA;
 
-  static bool attr_set[64] = {false};
-  int dev = 0;
-  (void)cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-    const cudaError_t ae = cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (ae != cudaSuccess) return fail(DF_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(ae));
-    if (dev >= 0 && dev < 64) attr_set[dev] = true;
-  }
   if (p.num_items < grid) grid = p.num_items;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  attention_kernel<true><<<grid, THREADS, SMEM_BYTES, s>>>(tm_q, tm_k, tm_v, p);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = cudaSuccess;
+  if (launch_option_value(DF_OPT_DECODE_KEYS_ON_LANES) != 0) {
+    // keys on the accumulator lanes: every softmax thread owns one key of a block
+    auto kernel = group <= 4 ? decode_attention_kernel<4> : (group <= 8 ? decode_attention_kernel<8> : decode_attention_kernel<16>);
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM_BYTES);
+    if (e != cudaSuccess) return fail(DF_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    kernel<<<grid, T_THREADS, T_SMEM_BYTES, s>>>(tm_q, tm_k, tm_v, p);
+  } else {
+    if (group > DECODE_MAX_GROUP)
+      return fail(DF_EUNSUPPORTED, "heads on the accumulator rows: at most %d query heads per key/value head (got %d)",
+                  DECODE_MAX_GROUP, group);
+    e = cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return fail(DF_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    attention_kernel<true><<<grid, THREADS, SMEM_BYTES, s>>>(tm_q, tm_k, tm_v, p);
+  }
+  e = cudaGetLastError();
   if (e != cudaSuccess) return fail(DF_ECUDA, "decode attention launch: %s", cudaGetErrorString(e));
   const int warps = batch * q_heads;
   attention_decode_merge_kernel<<<(warps * 32 + 255) / 256, 256, 0, s>>>(p.partial_o, p.partial_ml, seq_lens_dev, batch, q_heads,

@@ -22,6 +22,9 @@ void set_error(const char* fmt, ...) __attribute__((format(printf, 1, 2)));
 // set_error + return code, for one-line early exits.
 int fail(int code, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
 
+// Current value (0 / 1) of a launch-form option set with df_set_launch_option.
+int launch_option_value(int option);
+
 // Deadline for device-side waits, in nanoseconds from kernel start.
 unsigned long long timeout_ns();
 

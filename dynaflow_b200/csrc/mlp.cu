@@ -943,8 +943,9 @@ bool make_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t c
 
 // Launch-form options (df_set_launch_option): which of the bit-different but equally valid
 // forms of a launch is chosen. Process-wide, read at every launch.
-static std::atomic<int> g_launch_option[DF_OPT_COUNT_] = {{1}, {1}, {1}, {1}};
+static std::atomic<int> g_launch_option[DF_OPT_COUNT_] = {{1}, {1}, {1}, {1}, {1}};
 static int launch_option(int opt) { return g_launch_option[opt].load(std::memory_order_relaxed); }
+int launch_option_value(int option) { return (option >= 0 && option < DF_OPT_COUNT_) ? launch_option(option) : 0; }
 
 // Development knobs exist only in builds with -DDF_DEV_KNOBS (integers taken from the
 // environment on every launch, among them switches that skip the copies or the stores and so

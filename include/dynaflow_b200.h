@@ -127,12 +127,15 @@ int df_gateup_silu_bf16_ws(const void* x, const void* w_gate, const void* w_up, 
  *   DF_OPT_MLP_ONE_LAUNCH  df_mlp_gated_bf16 as one persistent launch where it applies
  *   DF_OPT_OPERAND_SWAP    operand-swapped tiles for launches of at most 128 rows
  *   DF_OPT_SPLIT_K_SMALL   launches of at most 128 rows as (tile, k range) CTAs that exchange
- *                          partial sums with bulk copies (with DF_OPT_STREAM_K off: one CTA per tile) */
+ *                          partial sums with bulk copies (with DF_OPT_STREAM_K off: one CTA per tile)
+ *   DF_OPT_DECODE_KEYS_ON_LANES  decode attention with both products transposed (a softmax thread per
+ *                          key of a block) instead of the query heads on the accumulator rows */
 #define DF_OPT_STREAM_K 0
 #define DF_OPT_MLP_ONE_LAUNCH 1
 #define DF_OPT_OPERAND_SWAP 2
 #define DF_OPT_SPLIT_K_SMALL 3
-#define DF_OPT_COUNT_ 4
+#define DF_OPT_DECODE_KEYS_ON_LANES 4
+#define DF_OPT_COUNT_ 5
 int df_set_launch_option(int option, int value);
 
 /* Bytes of scratch df_mlp_gated_bf16 needs: the bf16 intermediate h[M,I] plus one

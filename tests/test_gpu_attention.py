@@ -107,31 +107,80 @@ def test_rejects_unsupported_head_dim(native_lib):
 
 
 # ------------------------------------------------------------------ decode (split-KV)
-def _decode_case(ops, batch, max_len, hq, hkv, lens, seed, max_ctas=0):
+@pytest.fixture(params=[True, False], ids=["keys_on_lanes", "heads_on_rows"])
+def decode_form(request, ops):
+    """Both forms of the decode kernel: the transposed products (default) and the query heads on the
+    accumulator rows."""
+    ops.set_launch_option("decode_keys_on_lanes", request.param)
+    yield request.param
+    ops.set_launch_option("decode_keys_on_lanes", True)
+
+
+def _decode_case(ops, batch, max_len, hq, hkv, lens, seed, max_ctas=0, poison=False):
     from oracle import ops_oracle
 
     g = torch.Generator().manual_seed(seed)
     q = torch.randn(batch, hq * HD, generator=g).bfloat16()
     kc = torch.randn(batch, max_len, hkv * HD, generator=g).bfloat16()
     vc = torch.randn(batch, max_len, hkv * HD, generator=g).bfloat16()
+    if poison:   # what an allocator hands out: anything, NaN patterns included, past the end of a sequence
+        for b, n in enumerate(lens):
+            kc[b, n:] = float("nan")
+            vc[b, n:] = float("nan")
     out = torch.full((batch, hq * HD), float("nan"), dtype=torch.bfloat16, device="cuda")
     ws = torch.empty(ops.attention_decode_workspace_bytes(batch, hq, hkv, max_len), dtype=torch.uint8, device="cuda")
     sl = torch.tensor(lens, dtype=torch.int32, device="cuda")
     ops.attention_decode(q.cuda(), kc.cuda(), vc.cuda(), sl, out, ws, max_ctas=max_ctas)
     torch.cuda.synchronize()
     ops.check_status()
-    want = ops_oracle.decode_attention(q.view(batch, hq, HD), kc.view(batch, max_len, hkv, HD),
-                                       vc.view(batch, max_len, hkv, HD), lens).reshape(batch, hq * HD)
+    want = ops_oracle.decode_attention(q.view(batch, hq, HD), torch.nan_to_num(kc).view(batch, max_len, hkv, HD),
+                                       torch.nan_to_num(vc).view(batch, max_len, hkv, HD), lens).reshape(batch, hq * HD)
     return out.cpu(), want
 
 
 @pytest.mark.parametrize("batch,max_len,hq,hkv,lens", [
     (1, 128, 4, 1, [128]), (2, 256, 4, 1, [1, 256]), (3, 640, 8, 2, [640, 129, 300]), (5, 1024, 4, 4, [7, 1000, 512, 513, 1]),
-    (4, 4096, 4, 1, [4096, 4095, 2049, 100])])
-def test_decode_attention_matches_oracle(ops, batch, max_len, hq, hkv, lens):
+    (4, 4096, 4, 1, [4096, 4095, 2049, 100]), (2, 300, 3, 1, [300, 77]), (2, 384, 16, 2, [384, 130])])
+def test_decode_attention_matches_oracle(ops, batch, max_len, hq, hkv, lens, decode_form):
     got, want = _decode_case(ops, batch, max_len, hq, hkv, lens, 31)
     assert torch.isfinite(got.float()).all()
     assert _rel(got, want) <= TOL
+
+
+def test_decode_attention_ignores_what_lies_past_the_end_of_a_sequence(ops):
+    """Cache rows past seq_lens[b] are not the kernel's to read into the result: filled with NaN,
+    the output stays finite and equal to the oracle's."""
+    got, want = _decode_case(ops, 4, 1024, 8, 2, [1, 130, 1000, 513], 34, poison=True)
+    assert torch.isfinite(got.float()).all()
+    assert _rel(got, want) <= TOL
+
+
+def test_decode_attention_with_sixteen_heads_per_key_value_head(ops):
+    got, want = _decode_case(ops, 3, 512, 32, 2, [512, 65, 300], 35)
+    assert _rel(got, want) <= TOL
+
+
+def test_decode_attention_large_scores_rescale(ops):
+    """Scores that grow along the cache force the running reference maximum to move (the O^T rescale path)."""
+    from oracle import ops_oracle
+
+    batch, max_len, hq, hkv = 2, 1024, 4, 1
+    g = torch.Generator().manual_seed(36)
+    q = torch.randn(batch, hq * HD, generator=g).bfloat16()
+    ramp = torch.linspace(0.2, 3.0, max_len).view(1, max_len, 1)
+    kc = (q.view(batch, 1, hq, HD)[:, :, 0, :] * ramp).bfloat16().contiguous()     # keys aligned with head 0's query, growing
+    vc = torch.randn(batch, max_len, hkv * HD, generator=g).bfloat16()
+    lens = [1024, 700]
+    out = torch.empty(batch, hq * HD, dtype=torch.bfloat16, device="cuda")
+    ws = torch.empty(ops.attention_decode_workspace_bytes(batch, hq, hkv, max_len), dtype=torch.uint8, device="cuda")
+    sl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    ops.attention_decode(q.cuda(), kc.cuda(), vc.cuda(), sl, out, ws, max_ctas=2)   # long chunks: many blocks per item
+    torch.cuda.synchronize()
+    ops.check_status()
+    want = ops_oracle.decode_attention(q.view(batch, hq, HD), kc.view(batch, max_len, hkv, HD),
+                                       vc.view(batch, max_len, hkv, HD), lens).reshape(batch, hq * HD)
+    assert torch.isfinite(out.float()).all()
+    assert _rel(out.cpu(), want) <= TOL
 
 
 def test_decode_attention_on_few_ctas_is_within_tolerance(ops):
