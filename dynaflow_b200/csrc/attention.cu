@@ -698,6 +698,54 @@ __global__ void kv_cache_append_kernel(const __nv_bfloat16* __restrict__ k_new, 
   }
 }
 
+// Rotary embedding of the new token's query and key heads at position seq_lens[b] - 1, in place in the
+// fused qkv row [q heads | k heads | v heads], and the rotated keys and the values into the last
+// valid position of the caches. One thread per (sequence, head, 8 dims of the first half) for the
+// rotation, one per (sequence, 16-byte vector) for the values.
+__global__ void rope_append_kernel(__nv_bfloat16* __restrict__ qkv, int row_stride, const int* __restrict__ seq_lens, int batch,
+                                   int q_heads, int kv_heads, float theta, __nv_bfloat16* __restrict__ k_cache,
+                                   __nv_bfloat16* __restrict__ v_cache, int ld_cache, int max_len) {
+  constexpr int half = HD / 2, groups = half / 8;
+  const int rot_heads = q_heads + kv_heads;
+  const int v_vecs = kv_heads * HD / 8;
+  const int per_seq = rot_heads * groups + v_vecs;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < batch * per_seq; i += gridDim.x * blockDim.x) {
+    const int b = i / per_seq, r = i - b * per_seq;
+    const int pos = seq_lens[b] - 1;
+    const bool cached = pos >= 0 && pos < max_len;
+    const size_t cache_row = (static_cast<size_t>(b) * max_len + (cached ? pos : 0)) * ld_cache;
+    __nv_bfloat16* row = qkv + static_cast<size_t>(b) * row_stride;
+    if (r >= rot_heads * groups) {
+      const int v = r - rot_heads * groups;
+      if (cached) reinterpret_cast<uint4*>(v_cache + cache_row)[v] = reinterpret_cast<const uint4*>(row + rot_heads * HD)[v];
+      continue;
+    }
+    const int head = r / groups, gidx = r - head * groups;
+    __nv_bfloat16* base = row + head * HD + gidx * 8;
+    uint4 a = *reinterpret_cast<uint4*>(base), c4 = *reinterpret_cast<uint4*>(base + half);
+    __nv_bfloat16* x1 = reinterpret_cast<__nv_bfloat16*>(&a);
+    __nv_bfloat16* x2 = reinterpret_cast<__nv_bfloat16*>(&c4);
+    const float pf = static_cast<float>(pos);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int d = gidx * 8 + j;
+      const float inv_freq = powf(theta, -2.0f * static_cast<float>(d) / static_cast<float>(HD));
+      float sn, cs;
+      sincosf(pf * inv_freq, &sn, &cs);
+      const float u = __bfloat162float(x1[j]), v = __bfloat162float(x2[j]);
+      x1[j] = __float2bfloat16_rn(u * cs - v * sn);
+      x2[j] = __float2bfloat16_rn(v * cs + u * sn);
+    }
+    *reinterpret_cast<uint4*>(base) = a;
+    *reinterpret_cast<uint4*>(base + half) = c4;
+    if (head >= q_heads && cached) {
+      __nv_bfloat16* dst = k_cache + cache_row + (head - q_heads) * HD + gidx * 8;
+      *reinterpret_cast<uint4*>(dst) = a;
+      *reinterpret_cast<uint4*>(dst + half) = c4;
+    }
+  }
+}
+
 }  // namespace attn
 }  // namespace df
 
@@ -871,6 +919,28 @@ extern "C" int df_kv_cache_append_bf16(const void* k_new, const void* v_new, int
       static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), ld_cache, seq_lens_dev, batch, max_len, cols);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(DF_ECUDA, "kv append launch: %s", cudaGetErrorString(e));
+  return DF_OK;
+}
+
+extern "C" int df_rope_append_bf16(void* qkv, int row_stride, const int* seq_lens_dev, int batch, int q_heads, int kv_heads,
+                                   int head_dim, float theta, void* k_cache, void* v_cache, int ld_cache, int max_len,
+                                   void* stream) {
+  using namespace df;
+  if (qkv == nullptr || seq_lens_dev == nullptr || k_cache == nullptr || v_cache == nullptr)
+    return fail(DF_EINVAL, "NULL pointer argument");
+  if (head_dim != attn::HD) return fail(DF_EUNSUPPORTED, "head_dim must be %d (got %d)", attn::HD, head_dim);
+  const int cols = (q_heads + 2 * kv_heads) * head_dim;
+  if (batch <= 0 || max_len <= 0 || q_heads <= 0 || kv_heads <= 0 || row_stride < cols || (row_stride % 8) != 0 ||
+      ld_cache < kv_heads * head_dim || (ld_cache % 8) != 0)
+    return fail(DF_EINVAL, "bad shape: a qkv row of (q_heads + 2 kv_heads) * head_dim elements, strides multiples of 8");
+  if (((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15u) != 0)
+    return fail(DF_EINVAL, "qkv and the caches must be 16-byte aligned");
+  const int total = batch * ((q_heads + kv_heads) * (head_dim / 16) + kv_heads * head_dim / 8);
+  attn::rope_append_kernel<<<(total + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(qkv), row_stride, seq_lens_dev, batch, q_heads, kv_heads, theta,
+      static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), ld_cache, max_len);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(DF_ECUDA, "rope + append launch: %s", cudaGetErrorString(e));
   return DF_OK;
 }
 

@@ -230,10 +230,8 @@ class TensorParallelDecoder:
                 self.k_cache[li].copy_(torch.randn(shape[1:], generator=gen, device=dev))
                 self.v_cache[li].copy_(torch.randn(shape[1:], generator=gen, device=dev))
         self.seq_lens = torch.full((batch,), context_len, dtype=torch.int32, device=dev)
-        self.positions = self.seq_lens - 1
         rows = max(self.d_cuts[i + 1] - self.d_cuts[i] for i in range(n))
-        ws = ops.attention_decode_workspace_bytes(rows, self.qh, self.kvh, max_len)
-        self.attn_ws = [torch.empty(ws, dtype=torch.uint8, device=dev) for _ in range(n)]
+        self.attn_ws = [ops.attention_decode_workspace(rows, self.qh, self.kvh, max_len, dev) for _ in range(n)]
         per = s.vocab // self.world
         self.lm_head_shard = self.lm_head[self.rank * per:(self.rank + 1) * per].contiguous()
         self.logits = [torch.empty(rows, per, dtype=torch.bfloat16, device=dev) for _ in range(n)]
@@ -246,19 +244,13 @@ class TensorParallelDecoder:
         rows = hi - lo
         qkv = self.qkv[mb][:rows]
         ops.gemm_bf16(x, layer["wqkv"], out=qkv, max_ctas=self.gemm_max_ctas)
-        rc = self.lib.df_rope_bf16(qkv.data_ptr(), self.positions[lo:hi].data_ptr(), rows, self.qh + self.kvh, s.head_dim,
-                                   qkv.stride(0), s.rope_theta, torch.cuda.current_stream(self.device).cuda_stream)
-        if rc != 0:
-            raise RuntimeError(_native.last_error())
-        k_new = qkv[:, self.q_cols:self.q_cols + self.kv_cols]
-        v_new = qkv[:, self.q_cols + self.kv_cols:]
         kc, vc = self.k_cache[li, lo:hi], self.v_cache[li, lo:hi]
-        ops.kv_cache_append(k_new, v_new, kc, vc, self.seq_lens[lo:hi])
+        ops.rope_append(qkv, self.seq_lens[lo:hi], self.qh, self.kvh, kc, vc, s.rope_theta)
         attn = self.attn_out[mb][:rows]
         ops.attention_decode(qkv[:, :self.q_cols], kc, vc, self.seq_lens[lo:hi], attn, self.attn_ws[mb],
                              max_ctas=self.gemm_max_ctas)
         ops.gemm_bf16(attn, layer["wo"], out=self._partial(mb, rows), max_ctas=self.gemm_max_ctas)
-        self.launch_count += 6
+        self.launch_count += 4
 
     def decode_step(self, ids: torch.Tensor, skip_comm: bool = False, skip_compute: bool = False) -> list[torch.Tensor]:
         """One new token per sequence: ``ids [batch]`` -> per micro-batch this rank's slice of the
@@ -272,7 +264,6 @@ class TensorParallelDecoder:
         comm_stream = self.comm.stream if self.comm is not None else main
         xs: list = [None] * n
         rows_of = [self.d_cuts[i + 1] - self.d_cuts[i] for i in range(n)]
-        torch.sub(self.seq_lens, 1, out=self.positions)
         for mb in range(n):
             target = self.partial_local[mb][:rows_of[mb]] if self.comm is None else self.comm.partial(mb, rows_of[mb])
             torch.index_select(self.embed, 0, ids[self.d_cuts[mb]:self.d_cuts[mb + 1]], out=target)

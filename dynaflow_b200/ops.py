@@ -233,13 +233,33 @@ def attention_decode_workspace_bytes(batch: int, q_heads: int, kv_heads: int, ma
     return int(_native.load().df_attention_decode_workspace_bytes(batch, q_heads, kv_heads, max_len))
 
 
+def attention_decode_workspace(batch: int, q_heads: int, kv_heads: int, max_len: int,
+                               device: torch.device | str = "cuda") -> torch.Tensor:
+    """Scratch for ``attention_decode`` (the chunks' partial results); its contents are arbitrary."""
+    return torch.empty(attention_decode_workspace_bytes(batch, q_heads, kv_heads, max_len), dtype=torch.uint8, device=device)
+
+
+def rope_append(qkv: torch.Tensor, seq_lens: torch.Tensor, q_heads: int, kv_heads: int, k_cache: torch.Tensor,
+                v_cache: torch.Tensor, theta: float) -> None:
+    """Rotary embedding of the new token's query and key heads (position ``seq_lens[b] - 1``) in place in
+    ``qkv [B, (Hq + 2 Hkv) * 128]``, rotated keys and values into that position of the caches, one launch."""
+    _require_bf16_2d("qkv", qkv)
+    B = qkv.shape[0]
+    if k_cache.dim() != 3 or not k_cache.is_contiguous() or not v_cache.is_contiguous() or k_cache.shape[0] != B \
+            or k_cache.shape[2] != kv_heads * 128 or tuple(v_cache.shape) != tuple(k_cache.shape):
+        raise ValueError("expected contiguous bf16 caches [B, max_len, Hkv*128]")
+    rc = _native.load().df_rope_append_bf16(qkv.data_ptr(), qkv.stride(0), seq_lens.data_ptr(), B, q_heads, kv_heads, 128,
+                                            float(theta), k_cache.data_ptr(), v_cache.data_ptr(), k_cache.shape[2],
+                                            k_cache.shape[1], _stream_ptr(qkv))
+    _check(rc, "df_rope_append_bf16")
+
+
 def attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_lens: torch.Tensor,
                      out: torch.Tensor, workspace: torch.Tensor, *, scale: float | None = None,
                      max_ctas: int = 0) -> torch.Tensor:
     """One new token per sequence against its key/value cache. ``q, out [B, Hq*128]`` (2-D bf16
-    views, unit inner stride), ``k_cache, v_cache [B, max_len, Hkv*128]`` contiguous bf16 with the
-    rows beyond ``seq_lens[b]`` finite, ``seq_lens`` int32 on the device, ``workspace`` a uint8
-    tensor of ``attention_decode_workspace_bytes`` bytes."""
+    views, unit inner stride), ``k_cache, v_cache [B, max_len, Hkv*128]`` contiguous bf16,
+    ``seq_lens`` int32 on the device, ``workspace`` from ``attention_decode_workspace``."""
     _require_bf16_2d("q", q)
     _require_bf16_2d("out", out)
     hd = 128

@@ -378,14 +378,13 @@ int df_attention_prefill_bf16(const void* q, const void* k, const void* v, void*
  *   q        [batch, q_heads * 128] bf16, row stride ld_q (a column range of the fused qkv rows)
  *   k_cache, v_cache  [batch, max_len, kv_heads * 128] bf16, row stride ld_kv elements: sequence b
  *            owns rows [b * max_len, (b + 1) * max_len), of which the first seq_lens_dev[b] are valid
- *            (the new token's key and value included: see df_kv_cache_append_bf16). Rows of the
- *            cache that are not valid are read but masked: they must hold finite values
- *            (allocate the cache zeroed)
+ *            (the new token's key and value included: see df_rope_append_bf16). What lies past the
+ *            valid rows is read but never reaches the result, whatever it holds
  *   out      [batch, q_heads * 128] bf16
  * The keys of a sequence are cut into chunks that different CTAs process (split-KV); `workspace`
  * (df_attention_decode_workspace_bytes, 16-byte aligned, contents arbitrary) receives the chunks'
  * partial results, which a second small launch merges. seq_lens_dev stays in device memory, so a
- * captured graph follows growing sequences. head_dim must be 128, q_heads / kv_heads <= 8. */
+ * captured graph follows growing sequences. head_dim must be 128, q_heads / kv_heads <= 16. */
 size_t df_attention_decode_workspace_bytes(int batch, int q_heads, int kv_heads, int max_len);
 int df_attention_decode_bf16(const void* q, const void* k_cache, const void* v_cache, void* out,
                              const int* seq_lens_dev, int batch, int max_len, int q_heads, int kv_heads,
@@ -398,6 +397,16 @@ int df_attention_decode_bf16(const void* q, const void* k_cache, const void* v_c
 int df_kv_cache_append_bf16(const void* k_new, const void* v_new, int ld_new, void* k_cache, void* v_cache,
                             int ld_cache, const int* seq_lens_dev, int batch, int max_len, int kv_heads,
                             int head_dim, void* stream);
+
+/* The two steps before df_attention_decode_bf16 as one launch: rotary embedding (base theta, position
+ * seq_lens_dev[b] - 1) of the new token's query and key heads, in place in the fused qkv row
+ * [q heads | k heads | v heads] (row stride row_stride elements), and the rotated keys and the values
+ * into position seq_lens_dev[b] - 1 of the caches (layout as for df_attention_decode_bf16). Equal,
+ * bit for bit, to df_rope_bf16 on the first q_heads + kv_heads heads followed by
+ * df_kv_cache_append_bf16. head_dim must be 128. */
+int df_rope_append_bf16(void* qkv, int row_stride, const int* seq_lens_dev, int batch, int q_heads, int kv_heads,
+                        int head_dim, float theta, void* k_cache, void* v_cache, int ld_cache, int max_len,
+                        void* stream);
 
 /* Size of the library-owned scratch behind df_mlp_gated_bf16_static: 64 MiB of
  * static device memory, held by every GPU that loads the library until the

@@ -128,11 +128,15 @@ def _decode_case(ops, batch, max_len, hq, hkv, lens, seed, max_ctas=0, poison=Fa
             kc[b, n:] = float("nan")
             vc[b, n:] = float("nan")
     out = torch.full((batch, hq * HD), float("nan"), dtype=torch.bfloat16, device="cuda")
-    ws = torch.empty(ops.attention_decode_workspace_bytes(batch, hq, hkv, max_len), dtype=torch.uint8, device="cuda")
+    ws = ops.attention_decode_workspace(batch, hq, hkv, max_len)
     sl = torch.tensor(lens, dtype=torch.int32, device="cuda")
     ops.attention_decode(q.cuda(), kc.cuda(), vc.cuda(), sl, out, ws, max_ctas=max_ctas)
+    first = out.clone()
+    out.fill_(float("nan"))
+    ops.attention_decode(q.cuda(), kc.cuda(), vc.cuda(), sl, out, ws, max_ctas=max_ctas)   # bit-reproducible
     torch.cuda.synchronize()
     ops.check_status()
+    assert torch.equal(out, first)
     want = ops_oracle.decode_attention(q.view(batch, hq, HD), torch.nan_to_num(kc).view(batch, max_len, hkv, HD),
                                        torch.nan_to_num(vc).view(batch, max_len, hkv, HD), lens).reshape(batch, hq * HD)
     return out.cpu(), want
@@ -172,7 +176,7 @@ def test_decode_attention_large_scores_rescale(ops):
     vc = torch.randn(batch, max_len, hkv * HD, generator=g).bfloat16()
     lens = [1024, 700]
     out = torch.empty(batch, hq * HD, dtype=torch.bfloat16, device="cuda")
-    ws = torch.empty(ops.attention_decode_workspace_bytes(batch, hq, hkv, max_len), dtype=torch.uint8, device="cuda")
+    ws = ops.attention_decode_workspace(batch, hq, hkv, max_len)
     sl = torch.tensor(lens, dtype=torch.int32, device="cuda")
     ops.attention_decode(q.cuda(), kc.cuda(), vc.cuda(), sl, out, ws, max_ctas=2)   # long chunks: many blocks per item
     torch.cuda.synchronize()
@@ -190,6 +194,25 @@ def test_decode_attention_on_few_ctas_is_within_tolerance(ops):
     a, want = _decode_case(ops, 6, 1024, 8, 2, lens, 32)
     b, _ = _decode_case(ops, 6, 1024, 8, 2, lens, 32, max_ctas=3)
     assert _rel(a, want) <= TOL and _rel(b, want) <= TOL
+
+
+def test_rope_append_equals_rope_then_append(ops, native_lib):
+    g = torch.Generator().manual_seed(38)
+    B, max_len, hq, hkv = 5, 40, 4, 2
+    qkv = torch.randn(B, (hq + 2 * hkv) * HD, generator=g).bfloat16().cuda()
+    lens = [1, 40, 17, 2, 33]
+    sl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    ref = qkv.clone()
+    kc_ref = torch.zeros(B, max_len, hkv * HD, dtype=torch.bfloat16, device="cuda")
+    vc_ref = torch.zeros_like(kc_ref)
+    pos = (sl - 1).contiguous()
+    rc = native_lib.df_rope_bf16(ref.data_ptr(), pos.data_ptr(), B, hq + hkv, HD, ref.stride(0), 500000.0, None)
+    assert rc == 0
+    ops.kv_cache_append(ref[:, hq * HD:(hq + hkv) * HD], ref[:, (hq + hkv) * HD:], kc_ref, vc_ref, sl)
+    kc, vc = torch.zeros_like(kc_ref), torch.zeros_like(vc_ref)
+    ops.rope_append(qkv, sl, hq, hkv, kc, vc, 500000.0)
+    torch.cuda.synchronize()
+    assert torch.equal(qkv, ref) and torch.equal(kc, kc_ref) and torch.equal(vc, vc_ref)
 
 
 def test_kv_cache_append_writes_the_last_valid_position(ops):
