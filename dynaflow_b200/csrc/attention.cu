@@ -657,6 +657,8 @@ static int decode_chunk_blocks(int batch, int kv_heads, int max_len, int ctas) {
 __global__ void attention_decode_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                                               const int* __restrict__ seq_lens, int batch, int q_heads, int splits,
                                               int chunk_keys, int max_len, __nv_bfloat16* __restrict__ out, int ld_out) {
+  grid_dependency_wait();
+  grid_launch_dependents();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= batch * q_heads) return;
@@ -705,6 +707,8 @@ __global__ void kv_cache_append_kernel(const __nv_bfloat16* __restrict__ k_new, 
 __global__ void rope_append_kernel(__nv_bfloat16* __restrict__ qkv, int row_stride, const int* __restrict__ seq_lens, int batch,
                                    int q_heads, int kv_heads, float theta, __nv_bfloat16* __restrict__ k_cache,
                                    __nv_bfloat16* __restrict__ v_cache, int ld_cache, int max_len) {
+  grid_dependency_wait();
+  grid_launch_dependents();
   constexpr int half = HD / 2, groups = half / 8;
   const int rot_heads = q_heads + kv_heads;
   const int v_vecs = kv_heads * HD / 8;
@@ -884,7 +888,19 @@ extern "C" int df_attention_decode_bf16(const void* q, const void* k_cache, cons
     auto kernel = group <= 4 ? decode_attention_kernel<4> : (group <= 8 ? decode_attention_kernel<8> : decode_attention_kernel<16>);
     e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T_SMEM_BYTES);
     if (e != cudaSuccess) return fail(DF_ECUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    kernel<<<grid, T_THREADS, T_SMEM_BYTES, s>>>(tm_q, tm_k, tm_v, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(T_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = T_SMEM_BYTES;
+    cfg.stream = s;
+    cudaLaunchAttribute attr;
+    cfg.numAttrs = dependent_launch_attr(&attr);
+    cfg.attrs = &attr;
+    e = cudaLaunchKernelEx(&cfg, kernel, tm_q, tm_k, tm_v, p);
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();
+      return fail(DF_ECUDA, "decode attention launch: %s", cudaGetErrorString(e));
+    }
   } else {
     if (group > DECODE_MAX_GROUP)
       return fail(DF_EUNSUPPORTED, "heads on the accumulator rows: at most %d query heads per key/value head (got %d)",
@@ -896,10 +912,23 @@ extern "C" int df_attention_decode_bf16(const void* q, const void* k_cache, cons
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail(DF_ECUDA, "decode attention launch: %s", cudaGetErrorString(e));
   const int warps = batch * q_heads;
-  attention_decode_merge_kernel<<<(warps * 32 + 255) / 256, 256, 0, s>>>(p.partial_o, p.partial_ml, seq_lens_dev, batch, q_heads,
-                                                                       p.splits, p.chunk_blocks * BKV, max_len, p.out, ld_out);
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return fail(DF_ECUDA, "decode merge launch: %s", cudaGetErrorString(e));
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((warps * 32 + 255) / 256, 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = s;
+    cudaLaunchAttribute attr;
+    cfg.numAttrs = dependent_launch_attr(&attr);
+    cfg.attrs = &attr;
+    const float* po = p.partial_o;
+    const float* pml = p.partial_ml;
+    e = cudaLaunchKernelEx(&cfg, attention_decode_merge_kernel, po, pml, seq_lens_dev, batch, q_heads, p.splits,
+                           p.chunk_blocks * BKV, max_len, p.out, ld_out);
+  }
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(DF_ECUDA, "decode merge launch: %s", cudaGetErrorString(e));
+  }
   return DF_OK;
 }
 
@@ -936,11 +965,20 @@ extern "C" int df_rope_append_bf16(void* qkv, int row_stride, const int* seq_len
   if (((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15u) != 0)
     return fail(DF_EINVAL, "qkv and the caches must be 16-byte aligned");
   const int total = batch * ((q_heads + kv_heads) * (head_dim / 16) + kv_heads * head_dim / 8);
-  attn::rope_append_kernel<<<(total + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__nv_bfloat16*>(qkv), row_stride, seq_lens_dev, batch, q_heads, kv_heads, theta,
-      static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache), ld_cache, max_len);
-  const cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return fail(DF_ECUDA, "rope + append launch: %s", cudaGetErrorString(e));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((total + 127) / 128, 1, 1);
+  cfg.blockDim = dim3(128, 1, 1);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr;
+  cfg.numAttrs = dependent_launch_attr(&attr);
+  cfg.attrs = &attr;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, attn::rope_append_kernel, static_cast<__nv_bfloat16*>(qkv), row_stride,
+                                           seq_lens_dev, batch, q_heads, kv_heads, theta, static_cast<__nv_bfloat16*>(k_cache),
+                                           static_cast<__nv_bfloat16*>(v_cache), ld_cache, max_len);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(DF_ECUDA, "rope + append launch: %s", cudaGetErrorString(e));
+  }
   return DF_OK;
 }
 

@@ -112,6 +112,10 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 
   const uint32_t tmem_base = *tmem_slot;
   const Deadline dl{globaltimer_ns() + p.timeout_ns, abort_flag, p.status};
+  // everything above touched this CTA's own memories only; from here on the results of the kernel
+  // before this one in the stream (the new token's queries, keys and values) are read
+  grid_dependency_wait();
+  grid_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer

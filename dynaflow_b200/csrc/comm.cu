@@ -227,10 +227,12 @@ __global__ void __launch_bounds__(kCommThreads) add_rmsnorm_kernel(const __nv_bf
                                                                     const __nv_bfloat16* weight, int T, int H, float eps) {
   extern __shared__ uint4 s_weight[];
   const bool staged = H <= kMaxSmemHidden;
-  if (staged) {
+  if (staged) {  // the norm weight does not depend on the kernel before this one
     for (int v = threadIdx.x; v < (H >> 3); v += blockDim.x) s_weight[v] = reinterpret_cast<const uint4*>(weight)[v];
     __syncthreads();
   }
+  grid_dependency_wait();
+  grid_launch_dependents();
   const uint4* wv = staged ? s_weight : reinterpret_cast<const uint4*>(weight);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int row = blockIdx.x * kWarpsPerBlock + warp; row < T; row += gridDim.x * kWarpsPerBlock)
@@ -768,12 +770,21 @@ int df_add_rmsnorm_bf16(const void* y, const void* residual_in, void* residual_o
   int grid = (T + df::kWarpsPerBlock - 1) / df::kWarpsPerBlock;
   if (grid > sms * 8) grid = sms * 8;
   const size_t smem = H <= df::kMaxSmemHidden ? static_cast<size_t>(H) * 2 : 0;
-  df::add_rmsnorm_kernel<<<grid, df::kCommThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(residual_in),
-      static_cast<__nv_bfloat16*>(residual_out), static_cast<__nv_bfloat16*>(out),
-      static_cast<const __nv_bfloat16*>(weight), T, H, eps);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return df::fail(DF_ECUDA, "add_rmsnorm launch: %s", cudaGetErrorString(e));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(df::kCommThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr;
+  cfg.numAttrs = df::dependent_launch_attr(&attr);
+  cfg.attrs = &attr;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, df::add_rmsnorm_kernel, static_cast<const __nv_bfloat16*>(y),
+                                     static_cast<const __nv_bfloat16*>(residual_in), static_cast<__nv_bfloat16*>(residual_out),
+                                     static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(weight), T, H, eps);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return df::fail(DF_ECUDA, "add_rmsnorm launch: %s", cudaGetErrorString(e));
+  }
   return DF_OK;
 }
 

@@ -7,6 +7,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include "../../include/dynaflow_b200.h"
+
 namespace df {
 
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -24,6 +26,15 @@ int fail(int code, const char* fmt, ...) __attribute__((format(printf, 2, 3)));
 
 // Current value (0 / 1) of a launch-form option set with df_set_launch_option.
 int launch_option_value(int option);
+
+// Fills `attr` with the programmatic-serialization attribute when the DF_OPT_DEPENDENT_LAUNCH
+// option is on and returns how many attributes were written (0 or 1).
+inline int dependent_launch_attr(cudaLaunchAttribute* attr) {
+  if (launch_option_value(DF_OPT_DEPENDENT_LAUNCH) == 0) return 0;
+  attr->id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr->val.programmaticStreamSerializationAllowed = 1;
+  return 1;
+}
 
 // Deadline for device-side waits, in nanoseconds from kernel start.
 unsigned long long timeout_ns();

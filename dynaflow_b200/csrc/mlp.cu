@@ -943,7 +943,7 @@ bool make_map_bf16(CUtensorMap* map, const void* base, uint64_t rows, uint64_t c
 
 // Launch-form options (df_set_launch_option): which of the bit-different but equally valid
 // forms of a launch is chosen. Process-wide, read at every launch.
-static std::atomic<int> g_launch_option[DF_OPT_COUNT_] = {{1}, {1}, {1}, {1}, {1}};
+static std::atomic<int> g_launch_option[DF_OPT_COUNT_] = {{1}, {1}, {1}, {1}, {1}, {1}};
 static int launch_option(int opt) { return g_launch_option[opt].load(std::memory_order_relaxed); }
 int launch_option_value(int option) { return (option >= 0 && option < DF_OPT_COUNT_) ? launch_option(option) : 0; }
 

@@ -50,6 +50,16 @@ __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
 // Named barrier 1 over the four epilogue warps (128 threads) of a GEMM CTA.
 __device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
+// ------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-serialization attribute may start while the kernel
+// before it in the stream still runs. grid_dependency_wait() returns once that kernel (and, through
+// its own wait, every kernel before it) has completed and its writes are visible: nothing that the
+// earlier kernel produces may be read, and nothing it reads may be overwritten, before this call.
+// grid_launch_dependents() lets the NEXT kernel of the stream begin (its own wait then holds it
+// back until this grid has completed). Both do nothing in a launch without the attribute.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");

@@ -161,7 +161,21 @@ splitk_small_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const int y1 = (MODE == SMALL_GATEUP) ? n0 : n0 + p.bh;
       int stage = 0;
       uint32_t phase = 0;
-      for (int kb = kb0; kb < kb1; ++kb) {
+      // The weights do not depend on the kernel before this one in the stream: the first ring-full
+      // of weight boxes is on its way before the wait for that kernel's results, the rows of A follow it.
+      const int ahead = min(kb1 - kb0, p.stages);
+      for (int i = 0; i < ahead; ++i) {
+        uint8_t* sb = smem + i * stage_bytes + p.a_bytes;
+        mbar_expect_tx(&full[i], static_cast<uint32_t>(p.a_tx + 2 * b_box_bytes));
+        tma_load_2d(sb, &tm_b0, &full[i], (kb0 + i) * SK_BK, y0);
+        tma_load_2d(sb + b_box_bytes, &tm_b1, &full[i], (kb0 + i) * SK_BK, y1);
+      }
+      grid_dependency_wait();
+      grid_launch_dependents();
+      for (int i = 0; i < ahead; ++i) tma_load_2d(smem + i * stage_bytes, &tm_a, &full[i], (kb0 + i) * SK_BK, 0);
+      if (ahead == p.stages) phase ^= 1u;  // the ring has gone round once
+      stage = ahead == p.stages ? 0 : ahead;
+      for (int kb = kb0 + ahead; kb < kb1; ++kb) {
         if (!mbar_wait(&empty[stage], phase ^ 1u, dl, WHERE_SMALL_PRODUCER, blockIdx.x)) break;
         uint8_t* sa = smem + stage * stage_bytes;
         uint8_t* sb = sa + p.a_bytes;
@@ -216,6 +230,7 @@ splitk_small_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     bool ok = mbar_wait(tfull, 0u, dl, WHERE_SMALL_EPILOGUE, blockIdx.x);
     ok = __all_sync(0xffffffffu, ok);
     tc_fence_after();
+    grid_dependency_wait();  // long satisfied (the accumulator depends on rows of A fetched after the producer's wait)
     if (tid == 0) SMALL_STAMP(4);
     const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
 
@@ -475,15 +490,17 @@ static int launch_small_mode(const void* a, const void* b0, const void* b1, void
   cfg.blockDim = dim3(SK_THREADS, 1, 1);
   cfg.dynamicSmemBytes = best.smem_bytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr;
+  cudaLaunchAttribute attrs[2];
+  int n_attrs = dependent_launch_attr(&attrs[0]);
   if (best.splits > 1) {
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = best.splits;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
+    attrs[n_attrs].id = cudaLaunchAttributeClusterDimension;
+    attrs[n_attrs].val.clusterDim.x = best.splits;
+    attrs[n_attrs].val.clusterDim.y = 1;
+    attrs[n_attrs].val.clusterDim.z = 1;
+    ++n_attrs;
   }
+  cfg.attrs = attrs;
+  cfg.numAttrs = n_attrs;
   e = cudaLaunchKernelEx(&cfg, kernel, tm_a, tm_b0, tm_b1, p);
   if (e != cudaSuccess) {
     (void)cudaGetLastError();

@@ -72,7 +72,7 @@ def set_timeout_ms(ms: int) -> None:
         raise ValueError(_native.last_error())
 
 
-LAUNCH_OPTIONS = {"stream_k": 0, "mlp_one_launch": 1, "operand_swap": 2, "split_k_small": 3, "decode_keys_on_lanes": 4}
+LAUNCH_OPTIONS = {"stream_k": 0, "mlp_one_launch": 1, "operand_swap": 2, "split_k_small": 3, "decode_keys_on_lanes": 4, "dependent_launch": 5}
 
 
 def set_launch_option(name: str, on: bool) -> None:

@@ -129,13 +129,19 @@ int df_gateup_silu_bf16_ws(const void* x, const void* w_gate, const void* w_up, 
  *   DF_OPT_SPLIT_K_SMALL   launches of at most 128 rows as (tile, k range) CTAs that exchange
  *                          partial sums with bulk copies (with DF_OPT_STREAM_K off: one CTA per tile)
  *   DF_OPT_DECODE_KEYS_ON_LANES  decode attention with both products transposed (a softmax thread per
- *                          key of a block) instead of the query heads on the accumulator rows */
+ *                          key of a block) instead of the query heads on the accumulator rows
+ *   DF_OPT_DEPENDENT_LAUNCH  the kernels of a decode step (small-rows GEMM, rotary + append, decode
+ *                          attention and its merge, add + RMSNorm) are launched with programmatic
+ *                          stream serialization: each starts while its predecessor in the stream
+ *                          drains, sets itself up (the GEMM already fetches its weights) and only then
+ *                          waits for the predecessor's results. Results are identical either way. */
 #define DF_OPT_STREAM_K 0
 #define DF_OPT_MLP_ONE_LAUNCH 1
 #define DF_OPT_OPERAND_SWAP 2
 #define DF_OPT_SPLIT_K_SMALL 3
 #define DF_OPT_DECODE_KEYS_ON_LANES 4
-#define DF_OPT_COUNT_ 5
+#define DF_OPT_DEPENDENT_LAUNCH 5
+#define DF_OPT_COUNT_ 6
 int df_set_launch_option(int option, int value);
 
 /* Bytes of scratch df_mlp_gated_bf16 needs: the bf16 intermediate h[M,I] plus one

@@ -137,3 +137,15 @@ def test_decode_step_matches_pytorch_decoder(native_lib):
         ops.check_status()
         again = torch.cat(logits)
         assert torch.equal(again, got)
+    # without programmatic dependent launches (every kernel waits for its predecessor to drain before
+    # it starts): the same bits, eagerly and from a graph captured in that mode
+    ops.set_launch_option("dependent_launch", False)
+    try:
+        plain = torch.cat(dec.decode_step(last)).clone()
+        replay2, logits2 = dec.capture_decode(last)
+        replay2()
+        torch.cuda.synchronize()
+        ops.check_status()
+        assert torch.equal(plain, got) and torch.equal(torch.cat(logits2), got)
+    finally:
+        ops.set_launch_option("dependent_launch", True)
