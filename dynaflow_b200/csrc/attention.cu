@@ -653,7 +653,9 @@ static int decode_chunk_blocks(int batch, int kv_heads, int max_len, int ctas) {
 }
 
 // Merges the per-chunk results of the decode launch: out[b, head, :] = sum_s 2^(m_s - M) O_s /
-// sum_s 2^(m_s - M) l_s over the chunks that hold keys of sequence b. One warp per (b, head).
+// sum_s 2^(m_s - M) l_s over the chunks that hold keys of sequence b. One warp per (b, head); the
+// chunks' maxima and sums are fetched by one lane each and the partial rows eight chunks at a time,
+// so that a warp waits for two or three L2 round trips, not for two per chunk.
 __global__ void attention_decode_merge_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
                                               const int* __restrict__ seq_lens, int batch, int q_heads, int splits,
                                               int chunk_keys, int max_len, __nv_bfloat16* __restrict__ out, int ld_out) {
@@ -667,17 +669,44 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ partial_
   int used = (len + chunk_keys - 1) / chunk_keys;
   if (used > splits) used = splits;
   const size_t base = static_cast<size_t>(warp) * splits;
+  // pass 1: the largest reference maximum
   float big = -INFINITY;
-  for (int s = 0; s < used; ++s) big = fmaxf(big, partial_ml[2 * (base + s)]);
+  for (int s0 = 0; s0 < used; s0 += 32) {
+    const float m = s0 + lane < used ? partial_ml[2 * (base + s0 + lane)] : -INFINITY;
+    big = fmaxf(big, m);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, o));
+  // pass 2: weights and weighted rows, eight chunks in flight
   float acc[4] = {0.f, 0.f, 0.f, 0.f}, denom = 0.f;
-  for (int s = 0; s < used; ++s) {
-    const float wgt = ex2(partial_ml[2 * (base + s)] - big);
-    denom += wgt * partial_ml[2 * (base + s) + 1];
-    const float4 o = *reinterpret_cast<const float4*>(partial_o + (base + s) * HD + lane * 4);
-    acc[0] += wgt * o.x;
-    acc[1] += wgt * o.y;
-    acc[2] += wgt * o.z;
-    acc[3] += wgt * o.w;
+  for (int s0 = 0; s0 < used; s0 += 32) {
+    float wgt_l = 0.f, l_l = 0.f;  // this lane's chunk of the batch of 32
+    if (s0 + lane < used) {
+      const float2 ml = *reinterpret_cast<const float2*>(partial_ml + 2 * (base + s0 + lane));
+      wgt_l = ex2(ml.x - big);
+      l_l = ml.y;
+    }
+    const int n = min(32, used - s0);
+    for (int c0 = 0; c0 < n; c0 += 8) {
+      float4 o[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        o[c] = c0 + c < n ? *reinterpret_cast<const float4*>(partial_o + (base + s0 + c0 + c) * HD + lane * 4)
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        // chunks in index order: the same sum whatever the batch size
+        const float wgt = __shfl_sync(0xffffffffu, wgt_l, (c0 + c) & 31);
+        const float l = __shfl_sync(0xffffffffu, l_l, (c0 + c) & 31);
+        if (c0 + c < n) {
+          denom += wgt * l;
+          acc[0] += wgt * o[c].x;
+          acc[1] += wgt * o[c].y;
+          acc[2] += wgt * o[c].z;
+          acc[3] += wgt * o[c].w;
+        }
+      }
+    }
   }
   const float inv = used > 0 ? 1.0f / denom : 0.0f;
   uint2 packed = make_uint2(pack2(acc[0] * inv, acc[1] * inv), pack2(acc[2] * inv, acc[3] * inv));
