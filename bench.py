@@ -598,6 +598,72 @@ def decoder_block(args, sync, closers, rank: int, world: int, dev, plan: dict) -
     return out
 
 
+def small_gemm_block(args, rank: int, dev) -> dict:
+    """The projections of a decode step for one tensor-parallel rank (of ``--shard-of``, default 8): 128 rows
+    against the qkv, output, gate/up, down and vocabulary-shard weights, each shape as 24 launches on 24 copies of
+    its weights (more than L2) inside one CUDA graph, CUDA events around five replays. Per shape: microseconds per
+    launch (launch gap between dependent graph nodes included), weight bytes per second, and cuBLAS
+    (``torch.matmul``) on the same tensors beside it."""
+    import torch
+
+    from dynaflow_b200 import ops
+    from dynaflow_b200.decoder import DecoderShape
+
+    n = args.shard_of if args.shard_of > 1 else 8
+    s = DecoderShape()
+    rows = args.decode_batch // MICRO_BATCHES
+    q_cols, kv_cols = s.heads // n * s.head_dim, s.kv_heads // n * s.head_dim
+    shapes = [("qkv", q_cols + 2 * kv_cols, s.hidden), ("output", s.hidden, q_cols), ("down", s.hidden, s.intermediate // n),
+              ("vocabulary_shard", s.vocab // n, s.hidden)]
+    copies, replays = 24, 5
+    stream = torch.cuda.Stream(dev)
+
+    def timed(fn) -> float:
+        with torch.cuda.stream(stream):
+            for i in range(3):
+                fn(i)
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream, capture_error_mode="thread_local"):
+                for i in range(copies):
+                    fn(i)
+            graph.replay()
+            stream.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(replays):
+                graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+        return e0.elapsed_time(e1) * 1000.0 / (replays * copies)
+
+    gen = torch.Generator(device=dev).manual_seed(7)
+    out: dict = {"workload": f"decode-step projections, {rows} rows, one rank's share of {n}", "shapes": {}}
+    for name, N, K in shapes:
+        a = torch.randn(rows, K, device=dev, generator=gen).bfloat16()
+        w = [(torch.randn(N, K, device=dev, generator=gen) * 0.02).bfloat16() for _ in range(copies)]
+        c = torch.empty(rows, N, device=dev, dtype=torch.bfloat16)
+        us = timed(lambda i: ops.gemm_bf16(a, w[i], out=c))
+        want = a.float() @ w[copies - 1].float().T
+        err = ((c.float() - want).abs().max() / want.abs().max()).item()
+        us_lib = timed(lambda i: torch.matmul(a, w[i].T, out=c))
+        out["shapes"][name] = {"N": N, "K": K, "us": us, "weights_gbs": N * K * 2 / us / 1e3, "max_rel_err": err, "us_cublas": us_lib}
+        del w
+    H, I = s.hidden, s.intermediate // n
+    x = torch.randn(rows, H, device=dev, generator=gen).bfloat16()
+    wg = [(torch.randn(I, H, device=dev, generator=gen) * 0.02).bfloat16() for _ in range(copies)]
+    wu = [(torch.randn(I, H, device=dev, generator=gen) * 0.02).bfloat16() for _ in range(copies)]
+    h = torch.empty(rows, I, device=dev, dtype=torch.bfloat16)
+    us = timed(lambda i: ops.gateup_silu(x, wg[i], wu[i], out=h))
+    both = [torch.cat([wg[i], wu[i]]) for i in range(copies)]
+    c2 = torch.empty(rows, 2 * I, device=dev, dtype=torch.bfloat16)
+    us_lib = timed(lambda i: torch.matmul(x, both[i].T, out=c2))
+    out["shapes"]["gate_up_silu"] = {"N": 2 * I, "K": H, "us": us, "weights_gbs": 2 * I * H * 2 / us / 1e3,
+                                     "us_cublas": us_lib, "cublas_note": "one [2I, H] GEMM, no SiLU*mul"}
+    ops.check_status()
+    return out
+
+
 def decode_block(args, sync, closers, rank: int, world: int, dev, plan: dict) -> dict:
     """Llama-3-8B-shaped decoder in DECODE: batch 256, one new token per sequence, key/value cache of
     4096 positions per sequence filled N(0,1), two micro-batches of 128, tensor parallel over the
@@ -981,6 +1047,10 @@ def run_ours(args) -> None:
             line = decoder_block(args, sync, closers, rank, world, dev, comm_plan_applied(args, world))
         elif args.workload == "decode":
             line = decode_block(args, sync, closers, rank, world, dev, comm_plan_applied(args, world))
+        elif args.workload == "small-gemm":
+            if world != 1:
+                raise SystemExit("--workload small-gemm runs on one GPU")
+            line = small_gemm_block(args, rank, dev)
         else:
             line = measure(args, sync, closers, rank, world, local_rank, dev)
     except PeerFailed as exc:
@@ -1236,9 +1306,10 @@ def main() -> None:
     ap.add_argument("--kv-len", type=int, default=4096, help="decode: cached positions per sequence")
     ap.add_argument("--shard-of", type=int, default=1, help="decode on one GPU: run one rank's share of an N-way "
                     "tensor-parallel step (heads, key/value heads, intermediate and vocabulary divided by N, no reductions)")
-    ap.add_argument("--workload", choices=["mlp", "decoder", "decode", "moe"], default="mlp",
+    ap.add_argument("--workload", choices=["mlp", "decoder", "decode", "moe", "small-gemm"], default="mlp",
                     help="mlp: the fused gated-MLP layer step (the benchmark line, which also carries the decoder "
-                         "block); decoder / moe: that workload alone")
+                         "block); decoder / decode / moe: that workload alone; small-gemm: the decode step's "
+                         "projections per launch, one GPU")
     ap.add_argument("--layers", type=int, default=32, help="decoder: number of layers")
     ap.add_argument("--fused-norm", action="store_true", help="N > 1 chain: one-launch all-reduce+RMSNorm kernel")
     ap.add_argument("--no-sweep", action="store_true", help="skip the M sweep (profiling runs)")
