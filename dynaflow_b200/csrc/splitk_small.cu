@@ -446,6 +446,7 @@ static int launch_small_mode(const void* a, const void* b0, const void* b1, void
   best.cost = -1.0;
   for (int bh = 128; bh >= 32; bh /= 2) {
     if (force_bh > 0 && bh != force_bh) continue;
+    // powers of two only: clusters of 5 (28 gate/up tiles x 5 = 140 CTAs) measured 22 us against 13 us for clusters of 4
     for (int s = 1; s <= (allow_split ? SK_MAX_CLUSTER : 1); s *= 2) {
       if (force_splits > 0 && s != force_splits) continue;
       Plan cand;
