@@ -431,6 +431,22 @@ def leave_together(sync: RankSync, closers: list, error: str | None, learned: bo
     return error
 
 
+def last_block(sync: RankSync, fn) -> dict:
+    """Runs the LAST measured block of a run so that its failure does not lose what was measured
+    before: a rank whose block raises tells the others with one exchange (they are inside the block
+    and learn of it at their next synchronisation point, which raises ``PeerFailed`` there), and
+    every rank returns ``{"error": ...}`` in place of the block's figures. Nothing is launched on
+    the communicators after that; the run then leaves as usual."""
+    try:
+        return fn()
+    except PeerFailed as exc:  # learned at a synchronisation point: that exchange is consumed
+        return {"error": str(exc)}
+    except Exception as exc:  # noqa: BLE001
+        traceback.print_exc()
+        sync.reduce_max([0.0], fail=True)
+        return {"error": f"{type(exc).__name__}: {exc}"}
+
+
 def digest_of(t) -> float:
     """Order-independent exact checksum of a bf16 tensor's bits (fits a double exactly)."""
     import torch
@@ -700,6 +716,22 @@ def decode_block(args, sync, closers, rank: int, world: int, dev, plan: dict) ->
         sync.barrier()
         return sync.max_ms(a.elapsed_time(b) / reps)
 
+    # One step first, with the device-side waits cut to a second: a reduction whose peers never arrive then
+    # costs seconds, not minutes, and every rank learns of it here, before anything is timed.
+    ops.set_timeout_ms(1000)
+    trouble = None
+    try:
+        dec.decode_step(ids)
+        torch.cuda.synchronize()
+        ops.check_status()
+    except Exception as exc:  # noqa: BLE001 -- told to the other ranks just below
+        trouble = exc
+    finally:
+        ops.set_timeout_ms(2000)
+    sync.reduce_max([0.0], fail=trouble is not None)
+    if trouble is not None:   # the others know already (the exchange above): PeerFailed says "told"
+        raise PeerFailed(f"the first decode step failed on rank {rank}: {type(trouble).__name__}: {trouble}") from trouble
+
     t_eager = timed(lambda: dec.decode_step(ids), 3)
     ops.check_status()
     replay, logits = dec.capture_decode(ids)
@@ -968,7 +1000,8 @@ def measure(args, sync, closers, rank: int, world: int, local_rank: int, dev) ->
         decoder = decoder_block(args, sync, closers, rank, world, dev, plan)
         if world > 1:
             # (one GPU cannot hold the full key/value cache of this configuration beside the other workloads)
-            decode = decode_block(args, sync, closers, rank, world, dev, plan)
+            # The last block of the run: if it fails, the line keeps everything measured before it and says so.
+            decode = last_block(sync, lambda: decode_block(args, sync, closers, rank, world, dev, plan))
 
     peaks, peak_kind = measured_peaks()
     rows_mb = ROWS // MICRO_BATCHES

@@ -92,6 +92,20 @@ EXIT_WORKER = textwrap.dedent("""
         time.sleep(0.2 * rank)
         sync.barrier()
         sync.barrier()
+        if mode == "soft":
+            # the LAST block of a run fails on rank 2 after one of its synchronisation points: every rank gets
+            # {{"error": ...}} in place of the block's figures, and the run then leaves clean
+            def block():
+                sync.barrier()
+                if rank == 2:
+                    raise ValueError("rank 2 breaks in the last block")
+                time.sleep(0.1 * rank)
+                sync.barrier()
+                sync.max_ms(1.0)
+                return {{"figure": 1}}
+            got = bench.last_block(sync, block)
+            assert "error" in got and "figure" not in got, got
+            assert ("rank 2 breaks" in got["error"]) == (rank == 2), got
     except bench.PeerFailed as exc:
         error, learned = str(exc), True
     except Exception as exc:
@@ -124,10 +138,14 @@ def _run_exit_worker(tmp_path, mode, port):
 def test_ranks_leave_together_clean_and_after_a_failure(tmp_path):
     """bench.py's exit protocol on three gloo ranks: every host-side collective has one shape, so a rank
     that fails still pairs with the synchronisation its peers reach next; they learn of it there, and all
-    ranks run their closers between the same two meeting points and exit non-zero."""
+    ranks run their closers between the same two meeting points and exit non-zero. A failure inside the
+    run's last block (``last_block``) instead costs only that block: all ranks agree on it and leave clean."""
     ok = _run_exit_worker(tmp_path, "clean", 29741)
     assert ok.returncode == 0, (ok.stdout[-2000:], ok.stderr[-3000:])
     assert all(f"RANK{r}_LEFT_CLEAN" in ok.stdout for r in range(3))
+    soft = _run_exit_worker(tmp_path, "soft", 29743)
+    assert soft.returncode == 0, (soft.stdout[-2000:], soft.stderr[-3000:])
+    assert all(f"RANK{r}_LEFT_CLEAN" in soft.stdout for r in range(3))
     bad = _run_exit_worker(tmp_path, "fail", 29742)
     assert bad.returncode != 0
     assert all(f"RANK{r}_LEFT_WITH_ERROR" in bad.stdout for r in range(3)), (bad.stdout[-2000:], bad.stderr[-3000:])
