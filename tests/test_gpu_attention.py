@@ -187,6 +187,23 @@ def test_decode_attention_large_scores_rescale(ops):
     assert _rel(out.cpu(), want) <= TOL
 
 
+def test_decode_attention_random_shapes(ops):
+    """Twelve seeded random cases: batch, cache length, head grouping, ragged lengths, grid limit."""
+    import numpy as np
+
+    rng = np.random.default_rng(43)
+    for case in range(12):
+        hkv = int(rng.integers(1, 4))
+        group = int(rng.choice([1, 2, 3, 4, 5, 8, 12, 16]))
+        batch = int(rng.integers(1, 9))
+        max_len = int(rng.integers(1, 1200))
+        lens = [int(rng.integers(1, max_len + 1)) for _ in range(batch)]
+        max_ctas = 0 if case % 3 else int(rng.integers(1, 40))
+        got, want = _decode_case(ops, batch, max_len, hkv * group, hkv, lens, 500 + case, max_ctas=max_ctas, poison=case % 2 == 0)
+        assert torch.isfinite(got.float()).all(), (case, batch, max_len, hkv, group)
+        assert _rel(got, want) <= TOL, (case, batch, max_len, hkv, group, lens)
+
+
 def test_decode_attention_on_few_ctas_is_within_tolerance(ops):
     """Fewer CTAs cut the cache into fewer, longer chunks: another summation order, same result
     within tolerance."""

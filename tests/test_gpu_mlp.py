@@ -285,6 +285,35 @@ def test_split_k_small_gemm(ops, M, N, K):
         assert rel_err(other, out) <= 1e-2
 
 
+def test_split_k_small_random_shapes(ops):
+    """Forty seeded random shapes (1..128 rows, N and K any multiples of 8, strided operands and output, both the
+    plain and the gate/up form, a limited grid every fourth case) against fp32 products."""
+    rng = np.random.default_rng(41)
+    for case in range(40):
+        M = int(rng.integers(1, 129))
+        N = int(rng.integers(1, 600)) * 8
+        K = int(rng.integers(1, 400)) * 8
+        pad_a, pad_b, pad_c = (int(rng.integers(0, 3)) * 8 for _ in range(3))
+        a_full = _rand((M, K + pad_a), 1.0, 1000 + case).cuda()
+        b_full = _rand((N, K + pad_b), 0.05, 2000 + case).cuda()
+        a, b = a_full[:, pad_a:], b_full[:, :K]
+        canvas = torch.full((M + 1, N + pad_c + 8), 3.0, dtype=torch.bfloat16, device="cuda")
+        out = canvas[:M, pad_c:pad_c + N]
+        max_ctas = 0 if case % 4 else int(rng.integers(1, 60))
+        ops.gemm_bf16(a, b, out=out, max_ctas=max_ctas)
+        ops.check_status()
+        want = a.float() @ b.float().T
+        assert rel_err(out, want) <= TOL, (case, M, N, K, max_ctas)
+        assert torch.all(canvas[M:] == 3.0) and torch.all(canvas[:, :pad_c] == 3.0) and torch.all(canvas[:, pad_c + N:] == 3.0), (case, M, N, K)
+        if case % 2 == 0:
+            b2 = _rand((N, K), 0.05, 3000 + case).cuda()
+            h = ops.gateup_silu(a.contiguous(), b.contiguous(), b2, max_ctas=max_ctas)
+            ops.check_status()
+            g = (a.float() @ b.float().T).bfloat16().float()
+            u = (a.float() @ b2.float().T).bfloat16().float()
+            assert rel_err(h, torch.nn.functional.silu(g) * u) <= TOL, (case, M, N, K)
+
+
 @pytest.mark.parametrize("M", [2048, 8192, 16384])
 def test_benchmark_shapes_against_oracle_on_sampled_rows(ops, M):
     """The shapes every benchmark number is quoted on (hidden 4096, intermediate 14336; M rows in
