@@ -354,12 +354,17 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 #pragma unroll
       for (int h = 0; h < GROUP; ++h) {
         if (h >= p.group) break;
+        const float l_all = (red_sum[h] + red_sum[T_HEAD_ROWS + h]) + (red_sum[2 * T_HEAD_ROWS + h] + red_sum[3 * T_HEAD_ROWS + h]);
+        if (p.splits == 1) {
+          // the item is the whole sequence: its normalised rows are the result, nothing to merge
+          p.out[static_cast<size_t>(w.seq) * p.ld_out + (w.head + h) * HD + key] = __float2bfloat16_rn(__uint_as_float(o[h]) / l_all);
+          continue;
+        }
         const size_t slot = slot0 + static_cast<size_t>(h) * p.splits;
         p.partial_o[slot * HD + key] = __uint_as_float(o[h]);
         if (key == h) {
           p.partial_ml[2 * slot] = m_ref[h] * sl2;
-          p.partial_ml[2 * slot + 1] =
-              (red_sum[h] + red_sum[T_HEAD_ROWS + h]) + (red_sum[2 * T_HEAD_ROWS + h] + red_sum[3 * T_HEAD_ROWS + h]);
+          p.partial_ml[2 * slot + 1] = l_all;
         }
       }
       epilogue_bar_sync();  // red_sum is free for the next item
