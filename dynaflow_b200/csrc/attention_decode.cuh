@@ -112,8 +112,30 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
 
   const uint32_t tmem_base = *tmem_slot;
   const Deadline dl{globaltimer_ns() + p.timeout_ns, abort_flag, p.status};
-  // everything above touched this CTA's own memories only; from here on the results of the kernel
-  // before this one in the stream (the new token's queries, keys and values) are read
+  // Everything above touched this CTA's own memories only. The kernel before this one in the stream
+  // wrote the new token's queries and its keys and values (row seq_lens[b] - 1 of the caches):
+  // nothing of that is read before grid_dependency_wait(). The copy producer alone runs ahead of
+  // the wait, with key / value blocks that END before that row (they are from earlier steps).
+  int ahead_tiles = 0;
+  if (warp == 0 && lane == 0) {
+    for (int t = blockIdx.x; t < p.num_items; t += gridDim.x) {
+      Item w;
+      if (!item_coords<true>(p, t, w)) continue;
+      const int len_b = min(p.seq_lens[w.seq], p.max_len);
+      const int first_key = w.split * p.chunk_blocks * BKV;
+      const int old_blocks = max(0, min((len_b - 1 - first_key) / BKV, w.nb[0]));  // blocks that hold no key of the new token
+      ahead_tiles = min(2 * old_blocks, T_KV_SLOTS);
+      for (int u = 0; u < ahead_tiles; ++u) {
+        uint8_t* dst = sKV + u * TILE_BYTES;
+        const CUtensorMap* map = (u & 1) == 0 ? &tm_k : &tm_v;
+        const int krow = w.kv_row + (u >> 1) * BKV;
+        mbar_expect_tx(&kv_full[u], TILE_BYTES);
+        tma_load_2d(dst, map, &kv_full[u], w.kv_head * HD, krow);
+        tma_load_2d(dst + HALF_BYTES, map, &kv_full[u], w.kv_head * HD + 64, krow);
+      }
+      break;  // the first item only
+    }
+  }
   grid_dependency_wait();
   grid_launch_dependents();
 
@@ -134,6 +156,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_c
         for (int j = 0; j < w.nb[0] && ok; ++j) {
           const int krow = w.kv_row + j * BKV;
           for (int kv = 0; kv < 2; ++kv, ++u) {
+            if (u < static_cast<uint32_t>(ahead_tiles)) continue;  // requested before the wait (the first item's first tiles)
             const uint32_t slot = u % T_KV_SLOTS;
             if (!mbar_wait(&kv_empty[slot], ((u / T_KV_SLOTS) & 1u) ^ 1u, dl, WHERE_ATTN_PRODUCER, t)) {
               ok = false;

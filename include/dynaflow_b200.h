@@ -389,8 +389,14 @@ int df_attention_prefill_bf16(const void* q, const void* k, const void* v, void*
  *   out      [batch, q_heads * 128] bf16
  * The keys of a sequence are cut into chunks that different CTAs process (split-KV); `workspace`
  * (df_attention_decode_workspace_bytes, 16-byte aligned, contents arbitrary) receives the chunks'
- * partial results, which a second small launch merges. seq_lens_dev stays in device memory, so a
- * captured graph follows growing sequences. head_dim must be 128, q_heads / kv_heads <= 16. */
+ * partial results, which a second small launch merges (no cut, no second launch, when the (sequence,
+ * key/value head) pairs alone fill the SMs). seq_lens_dev stays in device memory, so a captured graph
+ * follows growing sequences. head_dim must be 128, q_heads / kv_heads <= 16.
+ * With DF_OPT_DEPENDENT_LAUNCH on, the launch starts while its predecessor in the stream drains and, before
+ * it waits for that kernel, already reads seq_lens_dev and cache blocks that end BEFORE row seq_lens_dev[b] - 1:
+ * a predecessor that itself releases its dependents early (griddepcontrol.launch_dependents: this library's
+ * kernels, e.g. df_rope_append_bf16, or a host kernel written that way) may write the new token's row and q,
+ * nothing else of these inputs. A predecessor that does not release early is a full dependency. */
 size_t df_attention_decode_workspace_bytes(int batch, int q_heads, int kv_heads, int max_len);
 int df_attention_decode_bf16(const void* q, const void* k_cache, const void* v_cache, void* out,
                              const int* seq_lens_dev, int batch, int max_len, int q_heads, int kv_heads,
