@@ -702,6 +702,8 @@ def decode_block(args, sync, closers, rank: int, world: int, dev, plan: dict) ->
                                 multicast=plan["comm"] == "multicast", gemm_max_ctas=plan["gemm_ctas"])
     closers.append(dec.close)
     dec.init_decode(batch, kv_len, context_len=kv_len, fill_seed=2)
+    if args.decode_streams >= 0:
+        dec.decode_streams_per_micro_batch = bool(args.decode_streams)
     ids = torch.randint(0, shape.vocab, (batch,), generator=torch.Generator().manual_seed(3)).to(dev)
 
     def timed(fn, reps):
@@ -1337,6 +1339,8 @@ def main() -> None:
                     help="moe workload: all-to-all puts / pulls of the routed rows, or all-gather / reduce-scatter of all rows")
     ap.add_argument("--decode-batch", type=int, default=256, help="decode: sequences per step")
     ap.add_argument("--kv-len", type=int, default=4096, help="decode: cached positions per sequence")
+    ap.add_argument("--decode-streams", type=int, default=-1, help="decode: 1 = one compute stream per micro-batch, 0 = one "
+                    "for all (default: per micro-batch on one GPU, one for all with reductions)")
     ap.add_argument("--shard-of", type=int, default=1, help="decode on one GPU: run one rank's share of an N-way "
                     "tensor-parallel step (heads, key/value heads, intermediate and vocabulary divided by N, no reductions)")
     ap.add_argument("--workload", choices=["mlp", "decoder", "decode", "moe", "small-gemm"], default="mlp",
