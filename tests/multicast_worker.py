@@ -57,6 +57,24 @@ def checks(comm, rank: int, world: int, dev: torch.device) -> None:
     lo, hi = comm.slice_bounds(T)
     rel = ((res_dev[lo:hi].cpu().float() - want_res[lo:hi].float()).abs().max() / want_res.float().abs().max()).item()
     assert rel <= 2e-2, f"rank {rank}: residual slice rel err {rel}"
+    # few rows per rank (a decode step): the form with a whole CTA per row; the result rows are the same rows
+    for small in (128, 40, 5):
+        comm.partial(1, small).copy_(parts[rank][:small])
+        res_small = residual[:small].to(dev)
+        out = comm.all_reduce_add_rmsnorm_sharded(1, small, res_small, weight.to(dev))
+        torch.cuda.synchronize()
+        ops.check_status()
+        rel = ((out.float().cpu() - want_out[:small].float()).abs().max() / want_out[:small].float().abs().max()).item()
+        assert rel <= 2e-2, f"rank {rank}: fused RMSNorm on {small} rows rel err {rel}"
+        lo, hi = comm.slice_bounds(small)
+        if hi > lo:
+            rel = ((res_small[lo:hi].cpu().float() - want_res[lo:hi].float()).abs().max()
+                   / want_res[:small].float().abs().max()).item()
+            assert rel <= 2e-2, f"rank {rank}: residual slice of {small} rows rel err {rel}"
+        digest = out.view(torch.int16).to(torch.int64).sum().reshape(1)
+        all_digests = [torch.zeros_like(digest) for _ in range(world)]
+        dist.all_gather(all_digests, digest)
+        assert all(int(d.item()) == int(digest.item()) for d in all_digests), f"ranks hold different results ({small} rows)"
     # an empty slice on some ranks (fewer rows than ranks) and a second slot in flight right after
     comm.partial(0, 3).copy_(parts[rank][:3])
     got = comm.all_reduce(0, 3)
