@@ -91,6 +91,7 @@ SIGNATURES: dict[str, tuple] = {
     "df_attention_decode_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "df_attention_decode_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp, _sz, _i, _vp, _vp]),
     "df_kv_cache_append_bf16": (_i, [_vp, _vp, _i, _vp, _vp, _i, _vp, _i, _i, _i, _i, _vp]),
+    "df_small_gemm_plan": (_i, [_i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "df_rope_append_bf16": (_i, [_vp, _i, _vp, _i, _i, _i, _i, _f, _vp, _vp, _i, _i, _vp]),
     "df_mlp_gated_bf16_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp]),
 }

@@ -437,24 +437,31 @@ static bool evaluate(int M, int N, int num_kb, bool gateup, int units, int bh, i
 
 }  // namespace
 
-template <int MODE>
-static int launch_small_mode(const void* a, const void* b0, const void* b1, void* c, int M, int N, int K, int lda, int ldb,
-                             int ldc, int units, bool allow_split, int force_bh, int force_splits,
-                             df_status_t* dev_status, cudaStream_t stream) {
+// The form a launch would take: the same search launch_small_mode() makes.
+static bool plan_small(int M, int N, int K, bool gateup, int units, bool allow_split, int force_bh, int force_splits,
+                       Plan* best) {
   const int num_kb = (K + SK_BK - 1) / SK_BK;
-  Plan best;
-  best.cost = -1.0;
+  best->cost = -1.0;
   for (int bh = 128; bh >= 32; bh /= 2) {
     if (force_bh > 0 && bh != force_bh) continue;
     // powers of two only: clusters of 5 (28 gate/up tiles x 5 = 140 CTAs) measured 22 us against 13 us for clusters of 4
     for (int s = 1; s <= (allow_split ? SK_MAX_CLUSTER : 1); s *= 2) {
       if (force_splits > 0 && s != force_splits) continue;
       Plan cand;
-      if (!evaluate(M, N, num_kb, MODE == SMALL_GATEUP, units, bh, s, &cand)) continue;
-      if (best.cost < 0.0 || cand.cost < best.cost) best = cand;
+      if (!evaluate(M, N, num_kb, gateup, units, bh, s, &cand)) continue;
+      if (best->cost < 0.0 || cand.cost < best->cost) *best = cand;
     }
   }
-  if (best.cost < 0.0) return DF_SMALL_NOT_APPLICABLE;
+  return best->cost >= 0.0;
+}
+
+template <int MODE>
+static int launch_small_mode(const void* a, const void* b0, const void* b1, void* c, int M, int N, int K, int lda, int ldb,
+                             int ldc, int units, bool allow_split, int force_bh, int force_splits,
+                             df_status_t* dev_status, cudaStream_t stream) {
+  const int num_kb = (K + SK_BK - 1) / SK_BK;
+  Plan best;
+  if (!plan_small(M, N, K, MODE == SMALL_GATEUP, units, allow_split, force_bh, force_splits, &best)) return DF_SMALL_NOT_APPLICABLE;
 
   CUtensorMap tm_a, tm_b0, tm_b1;
   if (!make_map_bf16(&tm_a, a, M, K, lda, M)) return DF_ECUDA;
@@ -522,3 +529,16 @@ int launch_small_rows(bool gateup, const void* a, const void* b0, const void* b1
 }
 
 }  // namespace df
+
+extern "C" int df_small_gemm_plan(int M, int N, int K, int gate_up, int sms, int* box_rows, int* k_splits, int* stages,
+                                  int* tiles, size_t* shared_bytes) {
+  if (M < 1 || M > 128 || N <= 0 || K <= 0 || sms <= 0) return df::fail(DF_EINVAL, "need 1 <= M <= 128 and positive N, K, sms");
+  df::Plan plan;
+  if (!df::plan_small(M, N, K, gate_up != 0, sms, true, 0, 0, &plan)) return df::fail(DF_EUNSUPPORTED, "no launch form fits this shape");
+  if (box_rows != nullptr) *box_rows = plan.bh;
+  if (k_splits != nullptr) *k_splits = plan.splits;
+  if (stages != nullptr) *stages = plan.stages;
+  if (tiles != nullptr) *tiles = plan.tiles;
+  if (shared_bytes != nullptr) *shared_bytes = static_cast<size_t>(plan.smem_bytes);
+  return DF_OK;
+}

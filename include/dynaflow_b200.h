@@ -120,6 +120,13 @@ int df_gateup_silu_bf16_ws(const void* x, const void* w_gate, const void* w_up, 
                            int ldx, int ldw, int ldh, int max_ctas, void* splitk_ws, size_t splitk_ws_bytes,
                            df_status_t* dev_status, void* stream);
 
+/* The form a GEMM launch of at most 128 rows takes on a device of `sms` SMs (no device needed: host arithmetic only):
+ * weight rows per operand box (32, 64 or 128), k ranges per output tile (= CTAs per thread-block cluster: 1, 2, 4 or 8),
+ * depth of the copy ring, output tiles, and the dynamic shared memory of a CTA. The grid is tiles * k_splits CTAs.
+ * Any output pointer may be NULL. */
+int df_small_gemm_plan(int M, int N, int K, int gate_up, int sms, int* box_rows, int* k_splits, int* stages, int* tiles,
+                       size_t* shared_bytes);
+
 /* Which of several equally valid forms a launch takes (all on by default). The forms differ in
  * the order of the fp32 summation, hence possibly in the last bf16 bit, never in validity; tests
  * switch them off to compare forms with each other. Process-wide; no counterpart in the reference.
