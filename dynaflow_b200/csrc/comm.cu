@@ -224,7 +224,8 @@ __device__ __forceinline__ void add_rmsnorm_row(const __nv_bfloat16* y_base, con
 // fused reduction as its own launch, for when the reduction itself runs on few CTAs.
 __global__ void __launch_bounds__(kCommThreads) add_rmsnorm_kernel(const __nv_bfloat16* y, const __nv_bfloat16* rin,
                                                                     __nv_bfloat16* rout, __nv_bfloat16* out,
-                                                                    const __nv_bfloat16* weight, int T, int H, float eps) {
+                                                                    const __nv_bfloat16* weight, int T, int H, float eps,
+                                                                    bool block_per_row) {
   extern __shared__ uint4 s_weight[];
   const bool staged = H <= kMaxSmemHidden;
   if (staged) {  // the norm weight does not depend on the kernel before this one
@@ -235,6 +236,64 @@ __global__ void __launch_bounds__(kCommThreads) add_rmsnorm_kernel(const __nv_bf
   grid_launch_dependents();
   const uint4* wv = staged ? s_weight : reinterpret_cast<const uint4*>(weight);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (block_per_row) {
+    // few rows (a decode step): a whole CTA per row, every load of the row in flight at once, the row kept in
+    // registers between the sum of squares and the scaling (the host chooses this form; H <= 8192)
+    constexpr int kRowVecs = 4;
+    __shared__ float s_part[kWarpsPerBlock];
+    const int nvec = H >> 3;
+    for (int row = blockIdx.x; row < T; row += gridDim.x) {
+      const size_t base = static_cast<size_t>(row) * H;
+      uint4 yv[kRowVecs], rv[kRowVecs];
+#pragma unroll
+      for (int k = 0; k < kRowVecs; ++k) {
+        const int v = threadIdx.x + k * kCommThreads;
+        if (v < nvec) {
+          yv[k] = __ldcg(reinterpret_cast<const uint4*>(y + base) + v);
+          rv[k] = rin != nullptr ? reinterpret_cast<const uint4*>(rin + base)[v] : make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      float f[kRowVecs][8];
+      float ss = 0.0f;
+#pragma unroll
+      for (int k = 0; k < kRowVecs; ++k) {
+        const int v = threadIdx.x + k * kCommThreads;
+        if (v < nvec) {
+          float fr[8];
+          unpack8(yv[k], f[k]);
+          unpack8(rv[k], fr);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[k][i] += fr[i];
+          const uint4 packed = pack8(f[k]);
+          reinterpret_cast<uint4*>(rout + base)[v] = packed;
+          unpack8(packed, f[k]);  // the sum of squares is taken over the rounded residual
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ss += f[k][i] * f[k][i];
+        }
+      }
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+      if (lane == 0) s_part[warp] = ss;
+      __syncthreads();
+      float total = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kWarpsPerBlock; ++w) total += s_part[w];
+      __syncthreads();
+      const float inv = rsqrtf(total / static_cast<float>(H) + eps);
+#pragma unroll
+      for (int k = 0; k < kRowVecs; ++k) {
+        const int v = threadIdx.x + k * kCommThreads;
+        if (v < nvec) {
+          float fw[8];
+          unpack8(wv[v], fw);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[k][i] = __bfloat162float(__float2bfloat16_rn(f[k][i] * inv)) * fw[i];
+          reinterpret_cast<uint4*>(out + base)[v] = pack8(f[k]);
+        }
+      }
+    }
+    return;
+  }
   for (int row = blockIdx.x * kWarpsPerBlock + warp; row < T; row += gridDim.x * kWarpsPerBlock)
     add_rmsnorm_row(y, rin, rout, out, wv, row, H, eps, lane);
 }
@@ -837,6 +896,9 @@ int df_add_rmsnorm_bf16(const void* y, const void* residual_in, void* residual_o
   if (sms <= 0) return df::fail(DF_ECUDA, "no CUDA device");
   int grid = (T + df::kWarpsPerBlock - 1) / df::kWarpsPerBlock;
   if (grid > sms * 8) grid = sms * 8;
+  // with a warp per row, fewer CTAs than SMs: a CTA per row instead (hidden <= 8192: four vectors per thread)
+  const bool block_per_row = grid < sms && H <= 8192;
+  if (block_per_row) grid = T < sms * 2 ? T : sms * 2;
   const size_t smem = H <= df::kMaxSmemHidden ? static_cast<size_t>(H) * 2 : 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
@@ -848,7 +910,8 @@ int df_add_rmsnorm_bf16(const void* y, const void* residual_in, void* residual_o
   cfg.attrs = &attr;
   cudaError_t e = cudaLaunchKernelEx(&cfg, df::add_rmsnorm_kernel, static_cast<const __nv_bfloat16*>(y),
                                      static_cast<const __nv_bfloat16*>(residual_in), static_cast<__nv_bfloat16*>(residual_out),
-                                     static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(weight), T, H, eps);
+                                     static_cast<__nv_bfloat16*>(out), static_cast<const __nv_bfloat16*>(weight), T, H, eps,
+                                     block_per_row);
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
     return df::fail(DF_ECUDA, "add_rmsnorm launch: %s", cudaGetErrorString(e));

@@ -97,12 +97,16 @@ def test_missing_peer_times_out_and_reports(comm_mod, native_lib):
         ops.set_timeout_ms(2000)
 
 
-def test_standalone_add_rmsnorm_equals_the_fused_second_half(comm_mod):
+@pytest.mark.parametrize("T", [300, 2000])
+def test_standalone_add_rmsnorm_equals_the_fused_second_half(comm_mod, T):
+    """2000 rows: a warp per row, the same arithmetic in the same order as the fused kernel's epilogue, so the same
+    bits. 300 rows: fewer warps than SMs, so a whole CTA takes a row (the sum of squares is then added up in another
+    order: the same residual bits, the normalised rows within one bf16 step)."""
     from dynaflow_b200 import ops
     from oracle import ops_oracle
 
     g = torch.Generator().manual_seed(21)
-    T, H = 300, 4096
+    H = 4096
     y = torch.randn(T, H, generator=g).bfloat16()
     res = torch.randn(T, H, generator=g).bfloat16()
     w = (1 + 0.1 * torch.randn(H, generator=g)).bfloat16()
@@ -114,14 +118,18 @@ def test_standalone_add_rmsnorm_equals_the_fused_second_half(comm_mod):
     assert torch.equal(res_dev.cpu(), want_res)
     assert _rel(out, want_out) <= TOL
     # bit-identical to the fused kernel's epilogue on the same sum
-    em = comm_mod.EmulatedComm(1, max_rows=512, hidden=H, n_ctas=4)
+    em = comm_mod.EmulatedComm(1, max_rows=2048, hidden=H, n_ctas=4)
     em.partial(0, T).copy_(y)
     out2 = [torch.empty(T, H, dtype=torch.bfloat16, device="cuda")]
     res2 = [res.cuda()]
     em.run(T, weight=w.cuda(), residual_in=res2, residual_out=res2, out=out2)
     torch.cuda.synchronize()
     ops.check_status()
-    assert torch.equal(out2[0], out) and torch.equal(res2[0], res_dev)
+    assert torch.equal(res2[0], res_dev)
+    if T >= 2000:
+        assert torch.equal(out2[0], out)
+    else:
+        assert torch.allclose(out2[0].float(), out.float(), rtol=2.0 ** -7, atol=1e-3)
     out0 = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
     res0 = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
     comm_mod.add_rmsnorm(y.cuda(), None, w.cuda(), out0, res0)   # no residual: r' = y
